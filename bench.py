@@ -1,0 +1,374 @@
+"""Benchmark of the fused sparse attention (SDDMM + softmax + SpMM over ACSR).
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation
+    python bench.py --impl reference --steps K --warmup W    # CPU restatement of the reference path
+
+Workload (default --config 5): B=8, H=64, L=32768, d=128, bf16, causal sliding window 1024,
+Q,K,V ~ N(0,1), softmax scale 1/sqrt(d); the 512 (batch, head) pairs are sharded over the ranks
+(strong scaling, no data-path collective).  One step = one pass of the fused kernel over the
+rank's heads.  Prints ONE JSON line on rank 0:
+
+  value         nnz-effective TFLOP/s (4*nnz*d flops per head) with inputs resident in HBM,
+                all ranks' work / max-over-ranks device time
+  e2e           the same metric through RegularAttention.forward_host: pinned host operands,
+                host->device and device->host copies inside the timed region
+  roofline      the fused kernel against the measured dense bf16 peak
+  cpu_baseline  the C restatement of the reference kernels on the host cores, bounded sample
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "triton-fun_b200", "SPLAT")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "nnz_effective_tflops_sddmm_softmax_spmm"
+UNIT = "TFLOP/s"
+
+#  cfg: (B, H, L, d, dtype name, pattern, p0, p1, input scale, seed, label)
+CONFIGS = {
+    2: (4, 16, 4096, 64, "fp16", "causal_windowed", 255, 0, 1.0, 1, "cfg2 local causal window 256"),
+    3: (2, 32, 8192, 128, "bf16", "strided", 64, 0, 1.0, 2, "cfg3 column stride 64"),
+    4: (1, 32, 16384, 128, "bf16", "dilated", 512, 2, 0.5, 3, "cfg4 dilated window 512x2"),
+    5: (8, 64, 32768, 128, "bf16", "causal_windowed", 1023, 0, 1.0, 4, "cfg5 long-context causal window 1024"),
+}
+KIND = {"blocked": 0, "windowed": 1, "causal_windowed": 2, "strided": 3, "dilated": 4}
+TORCH_DTYPE = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
+
+
+def nnz_per_head(cfg) -> int:
+    from oracle import acsr_oracle as ao  # integer arithmetic only; not on the measured path
+    B, H, L, d, dt, pat, p0, p1, *_ = CONFIGS[cfg]
+    return int(ao.pattern_rows(KIND[pat], L, p0, p1)[3].sum())
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"],
+                "tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=5)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(cfg, begin, end, device, chunk=64):
+    """Q, K, V for flat heads [begin, end); seeded per (config, 64-head chunk) so that the values do
+    not depend on how many GPUs share the work."""
+    B, H, L, d, dt, pat, p0, p1, spread, seed, _ = CONFIGS[cfg]
+    dtype = TORCH_DTYPE[dt]
+    outs = [torch.empty((1, end - begin, L, d), dtype=dtype, device=device) for _ in range(3)]
+    c0 = begin // chunk
+    while c0 * chunk < end:
+        g = torch.Generator(device=device).manual_seed(seed * 100003 + c0)
+        lo, hi = max(begin, c0 * chunk), min(end, (c0 + 1) * chunk)
+        for t in outs:
+            full = torch.randn((chunk, L, d), generator=g, device=device, dtype=torch.float32)
+            t[0, lo - begin:hi - begin] = (full[lo - c0 * chunk:hi - c0 * chunk] * spread).to(dtype)
+            del full
+        c0 += 1
+    return outs
+
+
+def cpu_reference_sample(cfg, budget_s=20.0, max_heads=16):
+    """Times the C restatement of the reference path (three kernels, S and P materialised) on the
+    host cores over a bounded number of heads of the workload.  Returns (tflops, heads, seconds,
+    threads)."""
+    import numpy as np
+    from oracle import acsr_oracle as ao
+    from oracle import c_oracle
+    B, H, L, d, dt, pat, p0, p1, spread, seed, _ = CONFIGS[cfg]
+    meta = ao.metadata_from_pattern(KIND[pat], L, p0, p1, 16)
+    T = meta["trailing_dim"]
+    rng = np.random.default_rng(seed)
+    one = [(rng.standard_normal((1, L, d), dtype=np.float32) * spread) for _ in range(3)]
+    scale = d ** -0.5
+    t0 = time.perf_counter()
+    c_oracle.attention(*one, meta, T, scale)
+    t1 = time.perf_counter() - t0
+    heads = int(max(1, min(max_heads, budget_s / max(t1, 1e-3))))
+    qkv = [np.repeat(x, heads, axis=0) for x in one] if heads > 1 else one
+    t0 = time.perf_counter()
+    c_oracle.attention(*qkv, meta, T, scale)
+    dt_s = time.perf_counter() - t0
+    flops = 4.0 * nnz_per_head(cfg) * d * heads
+    return flops / dt_s / 1e12, heads, dt_s, c_oracle.num_threads()
+
+
+def run_reference(args):
+    """The reference arm: the reference's algorithm on the host cores (C restatement; the Python +
+    Triton reference itself has no compiled form and is not present where this runs)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = args.config
+    B, H, L, d, dt, pat, p0, p1, spread, seed, label = CONFIGS[cfg]
+    budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    vals = []
+    heads = threads = 0
+    secs = 0.0
+    for i in range(args.warmup + args.steps):
+        v, heads, secs, threads = cpu_reference_sample(cfg, budget_s=budget)
+        if i >= args.warmup:
+            vals.append(v)
+    value = statistics.median(vals)
+    sample = f"{heads} of {B * H} heads per step ({secs:.2f} s), fp32, S and P materialised"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": label, "B": B, "H": H, "L": L, "d": d,
+                                        "pattern": pat, "p0": p0, "p1": p1},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import r_attention
+    import acsr_helpers as ah
+    import splat_native as n
+    from sharding import shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = args.config
+    B, H, L, d, dt, pat, p0, p1, spread, seed, label = CONFIGS[cfg]
+    dtype = TORCH_DTYPE[dt]
+    total_heads = B * H
+    begin, end = shard_range(total_heads, world, rank)
+    heads = end - begin
+    scale = d ** -0.5
+
+    mask = ah.PatternMask(KIND[pat], L, p0, p1)
+    t0 = time.perf_counter()
+    attn = r_attention.RegularAttention(1, L, heads, d, mask, 16, 16, dev, dtype, scale=scale,
+                                        path=n.PATH_BAND if args.path == "band" else
+                                        (n.PATH_GENERIC if args.path == "generic" else n.PATH_AUTO))
+    torch.cuda.synchronize()
+    metadata_ms = (time.perf_counter() - t0) * 1e3
+    nnz = int(attn.nnzs.double().sum().item())       # non-zeros per head, from the device metadata
+    flops_per_head = 4.0 * nnz * d
+    q, k, v = make_inputs(cfg, begin, end, dev)
+    kt = k.transpose(2, 3)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------------------------------------------------------- device-resident timing
+    for _ in range(args.warmup):
+        attn([q, kt, v])
+    attn.check_status()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ev[0].record()
+        for i in range(args.steps):
+            attn([q, kt, v])
+            ev[i + 1].record()
+        barrier()
+    attn.check_status()
+    per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    ms_total = ev[0].elapsed_time(ev[-1])
+    ms_step = ms_total / args.steps
+    t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step_max = float(t.item())
+    value = flops_per_head * total_heads / (ms_step_max * 1e-3) / 1e12
+
+    # ---------------------------------------------------------------- end to end, host operands
+    e2e = None
+    if not args.no_e2e:
+        import psutil
+        need = 4 * heads * L * d * q.element_size()
+        share_host = psutil.virtual_memory().available < 2.5 * need * max(1, world)
+        h_heads = min(heads, 32) if share_host else heads
+        host = [torch.empty((1, h_heads, L, d), dtype=dtype, pin_memory=True) for _ in range(4)]
+        for hbuf, src in zip(host[:3], (q, k, v)):
+            hbuf.copy_(src[:, :h_heads])
+        torch.cuda.synchronize()
+
+        def e2e_step():
+            if share_host:   # host RAM too small for the whole shard: re-send the same pinned chunk
+                for b in range(0, heads, h_heads):
+                    attn.forward_host(host[0], host[1], host[2], host[3], chunk_heads=h_heads)
+            else:
+                attn.forward_host(host[0], host[1], host[2], host[3], chunk_heads=32)
+
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        for _ in range(min(args.warmup, 2)):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        attn.check_status()
+        te = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        # result check of the host path on one head
+        if rank == 0:
+            q1, k1, v1 = (t[:, :1].contiguous() for t in (q, k, v))
+            o1 = torch.empty_like(q1)
+            n.attention_fused(q1, k1.transpose(2, 3), v1, o1, attn.sTod_linear_transformations,
+                              attn.sTod_translations, attn.nnzs, scale, attn.path, attn.plan)
+            assert torch.equal(o1.cpu(), host[3][:, :1]), "forward_host disagrees with forward"
+        e2e = {"value": flops_per_head * total_heads / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": 3 * heads * L * d * q.element_size() * world,
+               "d2h_bytes_per_step": heads * L * d * q.element_size() * world,
+               "ms_per_step": float(te.item()), "steps": e2e_steps,
+               "host_buffers": "one pinned 32-head chunk re-sent" if share_host else "whole shard pinned"}
+        del host
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N=1)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        val, h, secs, threads = cpu_reference_sample(cfg, budget_s=args.cpu_budget)
+        cpu = {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{h} of {total_heads} heads ({secs:.1f} s) of the same workload, fp32, "
+                         "three kernels with S and P materialised"}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        launch_ms = statistics.mean(per_launch)
+        achieved = flops_per_head * heads / (launch_ms * 1e-3) / 1e12
+        bytes_alg = 4.0 * L * d * q.element_size() * heads
+        t_flop = flops_per_head * heads / (peaks["tflops"] * 1e12)
+        t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
+        tensor_bound = t_flop >= t_hbm
+        if tensor_bound:
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops"]}
+        else:
+            gbs = bytes_alg / (launch_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"]}
+        roof.update({"traffic": None, "kernel": "attention_band_kernel", "peak_source": peaks["source"],
+                     "peak_kind": "burst", "launch_ms": launch_ms,
+                     "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"])
+                     if tensor_bound and peaks.get("tflops_sustained") else None,
+                     "algorithmic_gflop_per_launch": flops_per_head * heads / 1e9,
+                     "algorithmic_mb_per_launch": bytes_alg / 1e6})
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step_max, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": label, "B": B, "H": H, "L": L, "d": d, "pattern": pat, "p0": p0,
+                       "p1": p1, "softmax_scale": "1/sqrt(d)", "heads_per_gpu": heads,
+                       "parallelism": f"(batch,head) sharded over {world} GPU(s), no collective",
+                       "l2": "inputs larger than L2 (per-GPU Q+K+V = %.0f MB)" % (3 * heads * L * d * q.element_size() / 1e6),
+                       "path": args.path},
+            "e2e": e2e, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks.summary(),
+            "gpu_launches": args.steps * world, "metadata_build_ms": metadata_ms,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
+    ap.add_argument("--path", default="band", choices=["band", "generic", "auto"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

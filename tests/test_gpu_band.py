@@ -1,0 +1,105 @@
+"""GPU: the TMA + tcgen05 band kernel (both placements of the probability tile) against the CPU
+oracle, over window / blocked / strided / dilated patterns, ragged sizes and both 16-bit dtypes."""
+import pytest
+import torch
+
+from conftest import assert_close
+from oracle import acsr_oracle as ao
+from oracle import attention_oracle as at
+
+pytestmark = pytest.mark.gpu
+
+#        kind, L, p0, p1
+PATTERNS = [
+    (ao.PATTERN_CAUSAL_WINDOWED, 512, 63, 0),     # several key tiles, clipped head rows
+    (ao.PATTERN_CAUSAL_WINDOWED, 384, 255, 0),    # second Q tile of the last pair partly empty
+    (ao.PATTERN_CAUSAL_WINDOWED, 200, 31, 0),     # L < 256, not a multiple of 128
+    (ao.PATTERN_CAUSAL_WINDOWED, 1024, 1023, 0),  # dense causal
+    (ao.PATTERN_WINDOWED, 640, 100, 0),           # two-sided window
+    (ao.PATTERN_BLOCKED, 512, 96, 0),             # block-banded
+    (ao.PATTERN_STRIDED, 512, 4, 0),              # 4 residue classes of 128 rows; single-nnz rows
+    (ao.PATTERN_STRIDED, 1024, 64, 0),            # 64 classes of 16 rows
+    (ao.PATTERN_DILATED, 1024, 40, 2),            # two classes, window 40
+    (ao.PATTERN_DILATED, 768, 200, 3),            # three classes
+]
+
+
+def _run(kind, L, p0, p1, d, dtype, p_in_tmem, seed, BH=(1, 3), scale=None, spread=1.0):
+    import acsr_helpers as ah
+    import splat_native as n
+    torch.manual_seed(seed)
+    acsr = ah.create_acsr(ah.PatternMask(kind, L, p0, p1), 16, 0)
+    meta = ao.metadata_from_pattern(kind, L, p0, p1, 16)
+    B, H = BH
+    q, k, v = (torch.randn(B, H, L, d).mul_(spread).to(dtype) for _ in range(3))
+    scale = d ** -0.5 if scale is None else scale
+    out = torch.full((B, H, L, d), float("nan"), dtype=dtype, device="cuda")
+    n.debug_set_option(0, 1 if p_in_tmem else 0)
+    try:
+        n.attention_fused(q.cuda(), k.cuda().transpose(2, 3), v.cuda(), out, acsr[2], acsr[3], acsr[4],
+                          scale, n.PATH_BAND)
+        n.check_status_word(0)
+    finally:
+        n.debug_set_option(0, 1)
+    ref = at.attention_acsr(q, k.transpose(2, 3), v, meta, meta["trailing_dim"], scale)
+    return out, ref
+
+
+@pytest.mark.parametrize("p_in_tmem", [False, True])
+@pytest.mark.parametrize("d", [128, 64])
+def test_band_first_light(d, p_in_tmem):
+    """Smallest interesting case first: if this fails the rest is skipped by -x."""
+    out, ref = _run(ao.PATTERN_CAUSAL_WINDOWED, 256, 99, 0, d, torch.bfloat16, p_in_tmem, 1)
+    assert_close(out, ref, torch.bfloat16, f"first light d={d} tmem={p_in_tmem}")
+
+
+@pytest.mark.parametrize("p_in_tmem", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [128, 64])
+def test_band_patterns(d, dtype, p_in_tmem):
+    for i, (kind, L, p0, p1) in enumerate(PATTERNS):
+        out, ref = _run(kind, L, p0, p1, d, dtype, p_in_tmem, 100 + i)
+        assert_close(out, ref, dtype, f"pattern {(kind, L, p0, p1)} d={d} tmem={p_in_tmem}")
+
+
+def test_band_unscaled_scores_need_the_running_max():
+    """scale = 1 with d = 128 gives scores of sigma ~ 11: exercises the lazy rescale of O."""
+    for p_in_tmem in (False, True):
+        out, ref = _run(ao.PATTERN_CAUSAL_WINDOWED, 1024, 511, 0, 128, torch.bfloat16, p_in_tmem, 7,
+                        scale=1.0)
+        assert_close(out, ref, torch.bfloat16, f"unscaled tmem={p_in_tmem}")
+
+
+def test_band_matches_generic_kernel_and_is_deterministic():
+    import acsr_helpers as ah
+    import splat_native as n
+    torch.manual_seed(9)
+    L, d = 2048, 128
+    acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 300), 16, 0)
+    q, k, v = (torch.randn(2, 4, L, d, device="cuda").to(torch.bfloat16) for _ in range(3))
+    outs = []
+    for path in (n.PATH_BAND, n.PATH_BAND, n.PATH_GENERIC):
+        o = torch.empty_like(q)
+        n.attention_fused(q, k.transpose(2, 3), v, o, acsr[2], acsr[3], acsr[4], d ** -0.5, path)
+        outs.append(o)
+    n.check_status_word(0)
+    assert torch.equal(outs[0], outs[1])
+    assert_close(outs[0], outs[2].float(), torch.bfloat16, "band vs generic")
+
+
+def test_band_path_refuses_what_it_cannot_do():
+    import acsr_helpers as ah
+    import splat_native as n
+    L, d = 256, 128
+    acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 31), 16, 0)
+    q = torch.randn(1, 1, L, d, device="cuda").to(torch.bfloat16)
+    o = torch.empty_like(q)
+    kt_contig = q.transpose(2, 3).contiguous()
+    with pytest.raises(RuntimeError):      # contiguous K^T has no band path
+        n.attention_fused(q, kt_contig, q, o, acsr[2], acsr[3], acsr[4], 1.0, n.PATH_BAND)
+    n.attention_fused(q, kt_contig, q, o, acsr[2], acsr[3], acsr[4], 1.0, n.PATH_AUTO)  # falls back
+    q32 = q.float()
+    with pytest.raises(RuntimeError):      # fp32 has no band path
+        n.attention_fused(q32, q32.transpose(2, 3), q32, torch.empty_like(q32), acsr[2], acsr[3],
+                          acsr[4], 1.0, n.PATH_BAND)
+    torch.cuda.synchronize()

@@ -1,0 +1,183 @@
+"""GPU: SDDMM, softmax, SpMM and the fused CUDA-core chain through the reference-shaped launchers,
+against the CPU oracle and against the fixtures recorded from the reference kernels."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden_case
+from oracle import acsr_oracle as ao
+from oracle import attention_oracle as at
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def _acsr_for(name, golden_meta):
+    import acsr_helpers as ah
+    ref = golden_case(golden_meta, name)
+    kind, s, p0, p1, bh = ref["params"]
+    acsr = ah.create_acsr(ao.make_mask(kind, s, p0, p1), bh, 0)
+    return ref, acsr
+
+
+def _run_sddmm(mask_like, acsr, q, kt, dtype):
+    import r_sddmm
+    B, H, L, _ = q.shape
+    out, grid, tx, ty = r_sddmm.rsddmm_preamble(mask_like, (B, H, L, acsr[5]), 16, 16, 0, dtype)
+    out.fill_(float("nan"))
+    ret = r_sddmm.rsddmm_launcher(q, kt, out, acsr[0], acsr[1], acsr[2], acsr[3], acsr[5], acsr[4],
+                                  grid, tx, ty, 16, 16)
+    assert ret[0] is out and ret[1] is acsr[2] and ret[2] is acsr[3] and ret[3] is acsr[4]
+    return out
+
+
+def _run_softmax(mask_like, acsr, x, dtype, bsx=16, scale=None):
+    import r_softmax
+    B, H, L, T = x.shape
+    grid, out, _shape, pow2 = r_softmax.rsoftmax_preamble(mask_like, (B, H, L, T), bsx, 0, dtype)
+    out.fill_(float("nan"))
+    kw = {} if scale is None else {"scale": scale}
+    r_softmax.rsoftmax_launcher(x, out, acsr[0], acsr[1], acsr[2], acsr[3], T, pow2, acsr[4], grid,
+                                bsx, **kw)
+    return out
+
+
+def _run_spmm(mask_like, acsr, p, v, dtype):
+    import r_spmm
+    B, H, L, d = v.shape
+    out, grid, T = r_spmm.rspmm_preamble(mask_like, (B, H, L, d), 16, 16, 0, dtype)
+    assert T == acsr[5]
+    out.fill_(float("nan"))
+    r_spmm.rspmm_launcher(p, v, out, acsr[0], acsr[1], acsr[2], acsr[3], acsr[6], acsr[7], T,
+                          acsr[4], grid, 16, 16)
+    return out
+
+
+def test_reference_self_test_shapes(golden_meta, golden_reftests):
+    """The reference's nine self-test shapes with the recorded inputs: SDDMM and SpMM on integer
+    data are exact in fp32; softmax within fp32 rounding; padding slots are zero."""
+    g = golden_reftests
+    for name in (str(n) for n in g["names"]):
+        n, p, T = (int(v) for v in g[f"{name}/params"])
+        ref, acsr = _acsr_for(name, golden_meta)
+        mask = ao.blocked_mask(n, p)
+        _, _, nnz = ao.affine_ints(ref)
+        valid = torch.from_numpy(np.arange(T)[None, :] < nnz[:, None])
+        t = lambda key: torch.from_numpy(g[f"{name}/{key}"]).cuda()
+        s = _run_sddmm(mask, acsr, t("sddmm_x"), t("sddmm_y"), torch.float32).cpu()
+        assert torch.equal(s * valid, t("sddmm_out").cpu() * valid), name
+        assert (s * ~valid == 0).all(), name
+        sm = _run_softmax(mask, acsr, t("softmax_x"), torch.float32).cpu()
+        assert ((sm - t("softmax_out").cpu()) * valid).abs().max() < 1e-6, name
+        assert ((sm * valid).sum(-1) - 1).abs().max() < 1e-2, name     # the reference's own check
+        o = _run_spmm(mask, acsr, t("spmm_x"), t("spmm_y"), torch.float32).cpu()
+        assert torch.equal(o, t("spmm_out").cpu()), name
+
+
+def test_config1_against_reference_kernels(golden_meta, golden_cfg1):
+    c = golden_cfg1
+    ref, acsr = _acsr_for("causal_256_31", golden_meta)
+    mask = ao.causal_windowed_mask(256, 31)
+    q, k, v = (torch.from_numpy(c[x]).cuda() for x in "qkv")
+    kt = k.transpose(2, 3).contiguous()
+    s = _run_sddmm(mask, acsr, q, kt, torch.float32)
+    assert_close(s, torch.from_numpy(c["sddmm_out"]), torch.float32, "sddmm")
+    p = _run_softmax(mask, acsr, s, torch.float32, bsx=16)   # all rows, whatever BLOCK_SIZE_X says
+    assert_close(p, torch.from_numpy(c["softmax_out"]), torch.float32, "softmax")
+    o = _run_spmm(mask, acsr, p, v, torch.float32)
+    assert_close(o[:, :, :32], torch.from_numpy(c["spmm_out_rows_lt_d"]), torch.float32, "spmm")
+    s16 = _run_sddmm(mask, acsr, q.half(), kt.half(), torch.float16)
+    assert_close(s16, torch.from_numpy(c["sddmm_out_fp16"]).float(), torch.float16, "sddmm fp16")
+
+
+CASES = ["blocked_128_57", "windowed_100_7", "causal_300_127", "strided_256_64", "strided_200_7",
+         "dilated_256_8_2", "dilated_250_6_11", "causal_128_200", "windowed_33_0", "blocked_10_7"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kt_contiguous", [True, False])
+def test_ops_against_oracle(golden_meta, dtype, kt_contiguous):
+    torch.manual_seed(11)
+    for name in CASES:
+        ref, acsr = _acsr_for(name, golden_meta)
+        kind, L, p0, p1, _bh = ref["params"]
+        mask = ao.make_mask(kind, L, p0, p1)
+        T = ref["trailing_dim"]
+        for d in (32, 64, 24):
+            B, H = 2, 2
+            q, k, v = (torch.randn(B, H, L, d).to(dtype) for _ in range(3))
+            kt = k.transpose(2, 3).contiguous() if kt_contiguous else k.transpose(2, 3)
+            ktd = (k.cuda().transpose(2, 3).contiguous() if kt_contiguous else k.cuda().transpose(2, 3))
+            s = _run_sddmm(mask, acsr, q.cuda(), ktd, dtype)
+            s_ref = at.sddmm_acsr(q, kt, ref, T)
+            assert_close(s, s_ref, dtype, f"{name} d={d} sddmm")
+            scale = 1.0 / d ** 0.5
+            p = _run_softmax(mask, acsr, s, dtype, scale=scale)
+            p_ref = at.softmax_acsr(s.float().cpu(), ref, scale)
+            assert_close(p, p_ref, dtype, f"{name} d={d} softmax")
+            o = _run_spmm(mask, acsr, p, v.cuda(), dtype)
+            o_ref = at.spmm_acsr(p.float().cpu(), v, ref)
+            assert_close(o, o_ref, dtype, f"{name} d={d} spmm")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_fused_generic_against_oracle(golden_meta, dtype):
+    import splat_native as n
+    torch.manual_seed(12)
+    for name in CASES:
+        ref, acsr = _acsr_for(name, golden_meta)
+        L, T = ref["params"][1], ref["trailing_dim"]
+        for d, contig in ((32, False), (64, True), (128, False)):
+            q, k, v = (torch.randn(1, 3, L, d).to(dtype) for _ in range(3))
+            kt = k.transpose(2, 3)
+            ktd = k.cuda().transpose(2, 3).contiguous() if contig else k.cuda().transpose(2, 3)
+            out = torch.full((1, 3, L, d), float("nan"), dtype=dtype, device="cuda")
+            scale = 1.0 / d ** 0.5
+            n.attention_fused(q.cuda(), ktd, v.cuda(), out, acsr[2], acsr[3], acsr[4], scale,
+                              n.PATH_GENERIC)
+            o_ref = at.attention_acsr(q, kt, v, ref, T, scale)
+            assert_close(out, o_ref, dtype, f"{name} d={d} fused generic")
+
+
+def test_softmax_in_place_and_odd_trailing_dim():
+    """Trailing dims that break 16-byte rows take the scalar kernel; in-place is allowed."""
+    import acsr_helpers as ah
+    torch.manual_seed(3)
+    for L, p in ((50, 6), (40, 2)):
+        mask = ao.causal_windowed_mask(L, p)
+        acsr = ah.create_acsr(mask, 16, 0)
+        meta = ao.metadata_from_mask(mask, 16)
+        x = torch.randn(2, 2, L, acsr[5]) * 3
+        for dtype in DTYPES:
+            xd = x.to(dtype).cuda()
+            ref = at.softmax_acsr(x.to(dtype), meta)
+            import r_softmax
+            r_softmax.rsoftmax_launcher(xd, xd, acsr[0], acsr[1], acsr[2], acsr[3], acsr[5], 8, acsr[4],
+                                        (1, 1), 16)
+            assert_close(xd, ref, dtype, f"in-place softmax L={L}")
+
+
+def test_module_unfused_and_fused_agree_with_oracle(golden_meta):
+    import acsr_helpers as ah
+    import r_attention
+    torch.manual_seed(4)
+    ref = golden_case(golden_meta, "causal_256_31")
+    B, H, L, d = 1, 2, 256, 32
+    mask = ah.create_causal_windowed_mask(L, 31)
+    q, k, v = (torch.randn(B, H, L, d) for _ in range(3))
+    o_ref = at.attention_acsr(q, k.transpose(2, 3), v, ref, 32, 1.0)
+    for fused in (False, True):
+        attn = r_attention.RegularAttention(B, L, H, d, mask, 16, 16, 0, torch.float32, fused=fused)
+        out = attn([q.cuda(), k.cuda().transpose(2, 3), v.cuda()])
+        assert out is attn.rspmm_output                     # module-owned buffer, as in the reference
+        assert_close(out, o_ref, torch.float32, f"module fused={fused}")
+        assert attn([q.cuda(), k.cuda().transpose(2, 3), v.cuda()]) is out
+    # unit(): projections then attention
+    attn = r_attention.RegularAttention(B, L, H, d, mask, 16, 16, 0, torch.float32, scale=d ** -0.5)
+    x = torch.randn(B, L, H * d) * 0.2
+    w = [torch.randn(H * d, H, d) * 0.2 for _ in range(3)]
+    out = r_attention.unit(x.cuda(), x.cuda(), x.cuda(), *[t.cuda() for t in w], attn)
+    qp, kp, vp = (torch.einsum('bsd,dnh->bnsh', x, t) for t in w)
+    assert_close(out, at.attention_acsr(qp, kp.transpose(2, 3), vp, ref, 32, d ** -0.5),
+                 torch.float32, "unit")

@@ -1,0 +1,287 @@
+"""ctypes binding of libsplat_b200.so (the C ABI declared in include/splat_b200.h).
+
+There is no fallback: if the library is missing this module raises at import, and every wrapper
+turns a non-zero status into ``RuntimeError``.  Build the library with
+``python triton-fun_b200/build.py`` (nvcc, sm_100a).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG_DIR, "libsplat_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} not found: build it with `python {os.path.join(_PKG_DIR, 'build.py')}` "
+        "(this package has no CPU or eager fallback)")
+
+_lib = ctypes.CDLL(LIB_PATH)
+
+_i32, _i64, _f32, _vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
+
+# name -> argtypes; every function returns int32 except splat_status_string
+SIGNATURES = {
+    "splat_version": [],
+    "splat_mask_row_summary_u8": [_vp, _i64, _i64, _i64, _vp, _vp],
+    "splat_pattern_row_summary": [_i32, _i64, _i64, _i64, _vp, _vp],
+    "splat_pattern_mask_u8": [_i32, _i64, _i64, _i64, _vp, _i64, _vp],
+    "splat_acsr_from_row_summary": [_vp, _i64, _i64, _i32] + [_vp] * 8 + [_vp],
+    "splat_acsr_classify": [_vp, _vp, _vp, _i64, _vp, _vp],
+    "splat_sddmm": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
+                    _i32, _vp],
+    "splat_softmax": [_vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp],
+    "splat_spmm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
+    "splat_attention_fused": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                              _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
+    "splat_debug_set_option": [_i32, _i32],
+}
+for _name, _args in SIGNATURES.items():
+    _fn = getattr(_lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _i32
+_lib.splat_status_string.argtypes = [_i32]
+_lib.splat_status_string.restype = ctypes.c_char_p
+
+PATTERN_BLOCKED, PATTERN_WINDOWED, PATTERN_CAUSAL_WINDOWED, PATTERN_STRIDED, PATTERN_DILATED = range(5)
+PATH_AUTO, PATH_GENERIC, PATH_BAND = 0, 1, 2
+DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def status_string(code: int) -> str:
+    return _lib.splat_status_string(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what}: splat status {code} ({status_string(code)})")
+
+
+def version() -> int:
+    return _lib.splat_version()
+
+
+def resolve_device(gpu_id) -> torch.device:
+    """GPU_ID of the reference API: an int or a torch/cuda device.  'cpu' is rejected."""
+    dev = torch.device("cuda", gpu_id) if isinstance(gpu_id, int) else torch.device(gpu_id)
+    if dev.type != "cuda":
+        raise ValueError(f"device {gpu_id!r}: this implementation runs on CUDA devices only "
+                         "(there is no CPU path)")
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    return dev
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return DTYPES[dt]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dt}; expected float32, float16 or bfloat16") from None
+
+
+def _f32_vec(t: torch.Tensor, n: int, name: str) -> int:
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or t.numel() < n:
+        raise ValueError(f"{name} must be a contiguous float32 CUDA tensor of at least {n} elements")
+    return t.data_ptr()
+
+
+# ----------------------------------------------------------------------------------------------
+# metadata
+# ----------------------------------------------------------------------------------------------
+def mask_row_summary(mask_u8: torch.Tensor) -> torch.Tensor:
+    """(rows, cols) uint8 CUDA mask -> int32 (4, rows): first, second, last set column, count."""
+    assert mask_u8.is_cuda and mask_u8.dtype == torch.uint8 and mask_u8.dim() == 2
+    if mask_u8.stride(1) != 1:
+        mask_u8 = mask_u8.contiguous()
+    rows, cols = mask_u8.shape
+    out = torch.empty((4, rows), dtype=torch.int32, device=mask_u8.device)
+    with torch.cuda.device(mask_u8.device):
+        check(_lib.splat_mask_row_summary_u8(mask_u8.data_ptr(), rows, cols, mask_u8.stride(0),
+                                             out.data_ptr(), _stream(mask_u8.device)),
+              "splat_mask_row_summary_u8")
+    return out
+
+
+def pattern_row_summary(kind: int, n: int, p0: int, p1: int, dev: torch.device) -> torch.Tensor:
+    out = torch.empty((4, n), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.splat_pattern_row_summary(kind, n, p0, p1, out.data_ptr(), _stream(dev)),
+              "splat_pattern_row_summary")
+    return out
+
+
+def pattern_mask(kind: int, n: int, p0: int, p1: int, dev: torch.device) -> torch.Tensor:
+    out = torch.empty((n, n), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.splat_pattern_mask_u8(kind, n, p0, p1, out.data_ptr(), out.stride(0) if n else 0,
+                                         _stream(dev)), "splat_pattern_mask_u8")
+    return out
+
+
+def acsr_from_row_summary(rows_i32: torch.Tensor, n_cols: int, block_height: int):
+    """-> (dTos_lin, dTos_tr, sTod_lin, sTod_tr, nnzs, trailing_dim, span_start, span_end)."""
+    dev = rows_i32.device
+    n_rows = rows_i32.shape[1]
+    n_blocks = -(-n_rows // block_height)
+    vec = [torch.empty(n_rows, dtype=torch.float32, device=dev) for _ in range(5)]
+    spans = [torch.empty(n_blocks, dtype=torch.float32, device=dev) for _ in range(2)]
+    td = torch.empty(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.splat_acsr_from_row_summary(
+            rows_i32.data_ptr(), n_rows, n_cols, block_height, *[v.data_ptr() for v in vec],
+            spans[0].data_ptr(), spans[1].data_ptr(), td.data_ptr(), _stream(dev)),
+            "splat_acsr_from_row_summary")
+    return (*vec, int(td.item()), spans[0], spans[1])
+
+
+_PLAN_CACHE: dict = {}
+
+
+def classify(sTod_lin: torch.Tensor, sTod_tr: torch.Tensor, nnzs: torch.Tensor) -> tuple:
+    """Host copy of the 8 plan ints, cached per (tensor storage, version)."""
+    key = (sTod_lin.data_ptr(), sTod_tr.data_ptr(), nnzs.data_ptr(), sTod_lin._version,
+           sTod_tr._version, nnzs._version, nnzs.numel())
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None:
+        return hit
+    dev = nnzs.device
+    n = nnzs.numel()
+    plan = torch.empty(8, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.splat_acsr_classify(_f32_vec(sTod_lin, n, "sTod_lin"), _f32_vec(sTod_tr, n, "sTod_tr"),
+                                       _f32_vec(nnzs, n, "nnzs"), n, plan.data_ptr(), _stream(dev)),
+              "splat_acsr_classify")
+    host = tuple(int(v) for v in plan.cpu().tolist())
+    if len(_PLAN_CACHE) > 256:
+        _PLAN_CACHE.clear()
+    _PLAN_CACHE[key] = host
+    return host
+
+
+_STATUS_WORDS: dict = {}
+
+
+def status_word(dev: torch.device) -> torch.Tensor:
+    """Per-device int32 the band kernel sets when one of its bounded waits gives up."""
+    key = (dev.type, dev.index)
+    t = _STATUS_WORDS.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _STATUS_WORDS[key] = t
+    return t
+
+
+def check_status_word(dev) -> None:
+    """Synchronises the device; raises if a band kernel reported a timed-out wait (and clears it)."""
+    dev = resolve_device(dev)
+    w = status_word(dev)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"band kernel gave up on a device-side wait (code {code}): "
+                           f"{status_string(-5)}")
+
+
+# ----------------------------------------------------------------------------------------------
+# operators
+# ----------------------------------------------------------------------------------------------
+def _flat_bh(t: torch.Tensor, name: str):
+    """(B, H, X, Y) tensor whose (B, H) dims collapse -> (bh, stride_bh, stride_x, stride_y)."""
+    if t.dim() != 4:
+        raise ValueError(f"{name} must be 4-dimensional (batch, heads, ., .)")
+    B, H = t.shape[0], t.shape[1]
+    sb, sh, sx, sy = t.stride()
+    if B > 1 and H > 1 and sb != H * sh:
+        raise ValueError(f"{name}: batch and head dimensions must be collapsible (stride {t.stride()})")
+    stride_bh = sh if H > 1 else (sb if B > 1 else t.shape[2] * t.shape[3])
+    return B * H, stride_bh, sx, sy
+
+
+def _contig(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int) -> None:
+    dev = x.device
+    _contig(x, "x"); _contig(output, "output")
+    B, H, L, d = x.shape
+    bh, ksb, ksk, ksc = _flat_bh(y, "y")          # y is (B, H, d, n): dim 2 = k, dim 3 = column
+    n_cols = y.shape[3]
+    if y.shape[2] != d or bh != B * H or y.dtype != x.dtype or output.dtype != x.dtype:
+        raise ValueError("sddmm: inconsistent operand shapes or dtypes")
+    if tuple(output.shape) != (B, H, L, trailing_dim):
+        raise ValueError(f"sddmm: output must have shape {(B, H, L, trailing_dim)}")
+    with torch.cuda.device(dev):
+        check(_lib.splat_sddmm(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
+                               _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
+                               _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, trailing_dim,
+                               dtype_code(x.dtype), _stream(dev)), "splat_sddmm")
+
+
+def softmax(x, output, nnzs, trailing_dim: int, scale: float = 1.0) -> None:
+    dev = x.device
+    _contig(x, "x"); _contig(output, "output")
+    B, H, L, T = x.shape
+    if T != trailing_dim or output.shape != x.shape or output.dtype != x.dtype:
+        raise ValueError("softmax: inconsistent operand shapes or dtypes")
+    with torch.cuda.device(dev):
+        check(_lib.splat_softmax(x.data_ptr(), output.data_ptr(), _f32_vec(nnzs, L, "nnzs"), B * H,
+                                 L, T, float(scale), dtype_code(x.dtype), _stream(dev)),
+              "splat_softmax")
+
+
+def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int) -> None:
+    dev = x.device
+    _contig(x, "x"); _contig(y, "y"); _contig(output, "output")
+    B, H, L, T = x.shape
+    n_cols, d = y.shape[2], y.shape[3]
+    if T != trailing_dim or tuple(output.shape) != (B, H, L, d) or y.dtype != x.dtype or \
+            output.dtype != x.dtype or y.shape[:2] != x.shape[:2]:
+        raise ValueError("spmm: inconsistent operand shapes or dtypes")
+    with torch.cuda.device(dev):
+        check(_lib.splat_spmm(x.data_ptr(), y.data_ptr(), output.data_ptr(),
+                              _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
+                              _f32_vec(nnzs, L, "nnzs"), B * H, L, n_cols, d, T,
+                              dtype_code(x.dtype), _stream(dev)), "splat_spmm")
+
+
+def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.0,
+                    path: int = PATH_AUTO, plan=None) -> None:
+    """q, v, output (B,H,L,d) contiguous; kt (B,H,d,L) -- contiguous, or the transposed view of a
+    contiguous (B,H,L,d) tensor (required by the band path)."""
+    dev = q.device
+    _contig(q, "q"); _contig(v, "v"); _contig(output, "output")
+    B, H, L, d = q.shape
+    bh, ksb, ksk, ksc = _flat_bh(kt, "kt")
+    n_cols = kt.shape[3]
+    if kt.shape[2] != d or tuple(v.shape) != (B, H, n_cols, d) or output.shape != q.shape or \
+            len({q.dtype, kt.dtype, v.dtype, output.dtype}) != 1:
+        raise ValueError("attention: inconsistent operand shapes or dtypes")
+    plan_arr = None
+    if path != PATH_GENERIC:
+        if plan is None:
+            plan = classify(sTod_lin, sTod_tr, nnzs)
+        plan_arr = (ctypes.c_int32 * 8)(*plan)
+    sw = status_word(dev)
+    with torch.cuda.device(dev):
+        check(_lib.splat_attention_fused(
+            q.data_ptr(), kt.data_ptr(), ksb, ksc, ksk, v.data_ptr(), output.data_ptr(),
+            _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
+            _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, float(scale), dtype_code(q.dtype),
+            int(path), ctypes.cast(plan_arr, _vp) if plan_arr is not None else None,
+            sw.data_ptr(), _stream(dev)), "splat_attention_fused")
+    if os.environ.get("SPLAT_B200_DEBUG"):
+        check_status_word(dev)
+
+
+def debug_set_option(key: int, value: int) -> None:
+    check(_lib.splat_debug_set_option(key, value), "splat_debug_set_option")

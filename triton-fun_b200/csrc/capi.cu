@@ -1,0 +1,55 @@
+// Entry points that are not tied to one kernel file: version, status strings and the dispatch of
+// the fused attention call between the tensor-core band kernel and the general CUDA-core kernel.
+#include "common.cuh"
+
+namespace splat {
+int32_t attention_generic(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
+                          const void* v, void* o, const float* lin, const float* tr,
+                          const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
+                          float scale, int32_t dtype, cudaStream_t st);
+// Returns SPLAT_ERR_UNSUPPORTED_SHAPE (and launches nothing) when the problem does not qualify.
+int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
+                       const void* v, void* o, const float* lin, const float* tr,
+                       const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
+                       float scale, int32_t dtype, const int32_t* plan, int32_t* status_word,
+                       cudaStream_t st);
+}  // namespace splat
+
+extern "C" int32_t splat_version(void) { return SPLAT_B200_VERSION; }
+
+extern "C" const char* splat_status_string(int32_t status) {
+    switch (status) {
+        case SPLAT_OK: return "ok";
+        case SPLAT_ERR_BAD_ARG: return "bad argument (null pointer, negative or inconsistent size)";
+        case SPLAT_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype";
+        case SPLAT_ERR_MISALIGNED: return "pointer or stride is not aligned as the path requires";
+        case SPLAT_ERR_LAUNCH: return "CUDA error at kernel launch";
+        case SPLAT_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+        case SPLAT_ERR_UNSUPPORTED_SHAPE: return "shape not supported by the requested path";
+        case SPLAT_ERR_DRIVER: return "CUDA driver call failed (tensor map encode / entry point)";
+        case SPLAT_ERR_NO_DEVICE: return "no CUDA device";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int32_t splat_attention_fused(const void* q, const void* k, int64_t k_stride_bh,
+                                         int64_t k_stride_col, int64_t k_stride_k, const void* v,
+                                         void* o, const float* sTod_lin, const float* sTod_tr,
+                                         const float* nnzs, int64_t bh, int64_t n_rows,
+                                         int64_t n_cols, int64_t d, float scale, int32_t dtype,
+                                         int32_t path, const int32_t* plan_i32,
+                                         int32_t* status_word, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (path != SPLAT_PATH_AUTO && path != SPLAT_PATH_GENERIC && path != SPLAT_PATH_BAND)
+        return SPLAT_ERR_BAD_ARG;
+    if (path != SPLAT_PATH_GENERIC && plan_i32 != nullptr && status_word != nullptr) {
+        int32_t rc = splat::attention_band(q, k, k_stride_bh, k_stride_col, k_stride_k, v, o,
+                                           sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, scale,
+                                           dtype, plan_i32, status_word, st);
+        if (rc != SPLAT_ERR_UNSUPPORTED_SHAPE || path == SPLAT_PATH_BAND) return rc;
+    } else if (path == SPLAT_PATH_BAND) {
+        return SPLAT_ERR_BAD_ARG;
+    }
+    return splat::attention_generic(q, k, k_stride_bh, k_stride_col, k_stride_k, v, o, sTod_lin,
+                                    sTod_tr, nnzs, bh, n_rows, n_cols, d, scale, dtype, st);
+}
