@@ -210,7 +210,7 @@ def run_ours(args):
     cfg = args.config
     B, H, L, d, dt, pat, p0, p1, spread, seed, label = CONFIGS[cfg]
     dtype = TORCH_DTYPE[dt]
-    total_heads = B * H
+    total_heads = B * H if args.heads <= 0 else min(B * H, args.heads)
     begin, end = shard_range(total_heads, world, rank)
     heads = end - begin
     scale = d ** -0.5
@@ -336,7 +336,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms_step_max, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": dt, "data": "synthetic",
             "config": {"workload": label, "B": B, "H": H, "L": L, "d": d, "pattern": pat, "p0": p0,
-                       "p1": p1, "softmax_scale": "1/sqrt(d)", "heads_per_gpu": heads,
+                       "p1": p1, "softmax_scale": "1/sqrt(d)", "heads_per_gpu": heads, "heads_total": total_heads,
                        "parallelism": f"(batch,head) sharded over {world} GPU(s), no collective",
                        "l2": "inputs larger than L2 (per-GPU Q+K+V = %.0f MB)" % (3 * heads * L * d * q.element_size() / 1e6),
                        "path": args.path},
@@ -361,6 +361,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--heads", type=int, default=0,
+                    help="profiling aid: run only the first N (batch, head) pairs of the workload")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -141,16 +141,15 @@ def acsr_from_row_summary(rows_i32: torch.Tensor, n_cols: int, block_height: int
     return (*vec, int(td.item()), spans[0], spans[1])
 
 
-_PLAN_CACHE: dict = {}
-
-
 def classify(sTod_lin: torch.Tensor, sTod_tr: torch.Tensor, nnzs: torch.Tensor) -> tuple:
-    """Host copy of the 8 plan ints, cached per (tensor storage, version)."""
-    key = (sTod_lin.data_ptr(), sTod_tr.data_ptr(), nnzs.data_ptr(), sTod_lin._version,
-           sTod_tr._version, nnzs._version, nnzs.numel())
-    hit = _PLAN_CACHE.get(key)
-    if hit is not None:
-        return hit
+    """Host copy of the 8 plan ints of ``splat_acsr_classify``.  The result is remembered ON the
+    ``nnzs`` tensor object (with the identities and versions of all three tensors), so it lives
+    exactly as long as that metadata and is recomputed if any of them is modified in place."""
+    key = (id(sTod_lin), id(sTod_tr), sTod_lin._version, sTod_tr._version, nnzs._version,
+           nnzs.numel())
+    hit = getattr(nnzs, "_splat_plan", None)
+    if hit is not None and hit[0] == key:
+        return hit[1]
     dev = nnzs.device
     n = nnzs.numel()
     plan = torch.empty(8, dtype=torch.int32, device=dev)
@@ -159,9 +158,8 @@ def classify(sTod_lin: torch.Tensor, sTod_tr: torch.Tensor, nnzs: torch.Tensor) 
                                        _f32_vec(nnzs, n, "nnzs"), n, plan.data_ptr(), _stream(dev)),
               "splat_acsr_classify")
     host = tuple(int(v) for v in plan.cpu().tolist())
-    if len(_PLAN_CACHE) > 256:
-        _PLAN_CACHE.clear()
-    _PLAN_CACHE[key] = host
+    # keep the two companions alive with the cache entry so their ids cannot be reused
+    nnzs._splat_plan = (key, host, sTod_lin, sTod_tr)
     return host
 
 
