@@ -87,6 +87,24 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// packed fp32x2 arithmetic (one issue slot for two lanes of work)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    uint64_t ua = *reinterpret_cast<uint64_t*>(&a), ub = *reinterpret_cast<uint64_t*>(&b),
+             uc = *reinterpret_cast<uint64_t*>(&c), ud;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(ud) : "l"(ua), "l"(ub), "l"(uc));
+    return *reinterpret_cast<float2*>(&ud);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    uint64_t ua = *reinterpret_cast<uint64_t*>(&a), ub = *reinterpret_cast<uint64_t*>(&b), ud;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(ud) : "l"(ua), "l"(ub));
+    return *reinterpret_cast<float2*>(&ud);
+}
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
@@ -322,7 +340,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         float m_used = -INFINITY, l_sum = 0.f;
         uint32_t s_phase = 0;
         bool ok = true;
-        uint32_t r[32];
+        const float sc = p.scale_log2;
         for (int n = rlo[x]; n < rhi[x]; ++n) {
             ok = mbar_wait(&ctrl->s_ready[x], s_phase, status, kErrSReady);
             ok = __all_sync(0xffffffffu, ok);  // keep the warp together for the aligned tcgen05 ops
@@ -332,74 +350,78 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const int c0 = n * kTile;
             const int v_lo = my_a - c0;               // valid columns of this tile: [v_lo, v_hi)
             const int v_hi = my_n > 0 ? my_a + my_n - c0 : INT_MIN;
-            // pass 1: row maximum over valid columns
-            float mt = -INFINITY;
+            const bool warp_full = __all_sync(0xffffffffu, v_lo <= 0 && v_hi >= kTile);
+
+            // the whole score row of this thread, one wait for the four loads
+            uint32_t r[kTile];
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                tmem_ld32(s_addr + ch * 32, r);
-                tmem_ld_wait();
+            for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_addr + ch * 32, r + ch * 32);
+            tmem_ld_wait();
+            if (!warp_full) {   // band edge: columns outside [v_lo, v_hi) become -inf (exp2 -> 0)
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int c = ch * 32 + j;
-                    const float v = __uint_as_float(r[j]);
-                    mt = fmaxf(mt, (c >= v_lo && c < v_hi) ? v : -INFINITY);
-                }
+                for (int j = 0; j < kTile; ++j)
+                    r[j] = (j >= v_lo && j < v_hi) ? r[j] : 0xff800000u;
             }
-            const float m_new = fmaxf(m_used, mt * p.scale_log2);
+            // row maximum, four independent chains of 3-input max
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < kTile; j += 8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    mx[c] = fmax3(mx[c], __uint_as_float(r[j + 2 * c]), __uint_as_float(r[j + 2 * c + 1]));
+            }
+            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const float m_new = fmaxf(m_used, mt * sc);
             const bool need = (m_new - m_used) > kRescaleThreshold;  // false when both are -inf
-            if (__any_sync(0xffffffffu, need)) {
-                const float corr = need ? ex2(m_used - m_new) : 1.f;
-                if (need) m_used = m_new;
-                l_sum *= corr;
-                if (n > rlo[x]) {
-#pragma unroll
-                    for (int ch = 0; ch < D / 32; ++ch) {
-                        tmem_ld32(o_addr + ch * 32, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
-                        tmem_st32(o_addr + ch * 32, r);
-                    }
-                    tmem_st_wait();
-                }
-            }
+            const float corr = need ? ex2(m_used - m_new) : 1.f;
+            if (need) m_used = m_new;
+            l_sum *= corr;
             const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-            // pass 2: probabilities, row sum, P written for the second MMA
-            float part = 0.f;
+
+            // probabilities: exp2(s*c - m) with packed fp32x2 FMAs, row sum, 16-bit pack in place
+            const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-m_eff, -m_eff);
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                tmem_ld32(s_addr + ch * 32, r);
-                tmem_ld_wait();
-                uint32_t pk[16];
+            for (int j = 0; j < kTile; j += 4) {
+                float2 a0 = fma2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc2, nm2);
+                float2 a1 = fma2(make_float2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), sc2, nm2);
+                a0.x = ex2(a0.x); a0.y = ex2(a0.y); a1.x = ex2(a1.x); a1.y = ex2(a1.y);
+                acc0 = add2(acc0, a0);
+                acc1 = add2(acc1, a1);
+                r[j >> 1] = pack2<T>(a0.x, a0.y);
+                r[(j >> 1) + 1] = pack2<T>(a1.x, a1.y);
+            }
+            l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+            if constexpr (kPTmem) {
+                tmem_st32(s_addr, r);            // P (64 packed columns) over the first half of S
+                tmem_st32(s_addr + 32, r + 32);
+            } else {
+                // K-major, 128-byte rows, 16-byte chunk index XOR (row mod 8)
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int c = ch * 32 + j;
-                    float e0 = ex2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_eff));
-                    float e1 = ex2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_eff));
-                    e0 = (c >= v_lo && c < v_hi) ? e0 : 0.f;
-                    e1 = (c + 1 >= v_lo && c + 1 < v_hi) ? e1 : 0.f;
-                    part += e0 + e1;
-                    pk[j >> 1] = pack2<T>(e0, e1);
-                }
-                if constexpr (kPTmem) {
-                    tmem_st16(s_addr + ch * 16, pk);
-                } else {
-                    // K-major, 128-byte rows, 16-byte chunk index XOR (row mod 8)
-                    uint8_t* prow = s_p + x * L::kPBytes + (ch >> 1) * kSubBytes + t * 128;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int cc = (ch & 1) * 4 + q4;
-                        *reinterpret_cast<uint4*>(prow + ((cc ^ (t & 7)) << 4)) =
-                            make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-                    }
+                for (int cc16 = 0; cc16 < 16; ++cc16) {
+                    uint8_t* prow = s_p + x * L::kPBytes + (cc16 >> 3) * kSubBytes + t * 128;
+                    *reinterpret_cast<uint4*>(prow + (((cc16 & 7) ^ (t & 7)) << 4)) =
+                        make_uint4(r[cc16 * 4], r[cc16 * 4 + 1], r[cc16 * 4 + 2], r[cc16 * 4 + 3]);
                 }
             }
-            l_sum += part;
+            // lazy rescale of the accumulator (rare): only when some row's maximum moved by > 2^8
+            if (__any_sync(0xffffffffu, need) && n > rlo[x]) {
+                uint32_t o[32];
+#pragma unroll
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    tmem_ld32(o_addr + ch * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                    tmem_st32(o_addr + ch * 32, o);
+                }
+            }
             if constexpr (kPTmem) tmem_st_wait();
-            else fence_proxy_async_smem();
+            else { tmem_st_wait(); fence_proxy_async_smem(); }
             tc_fence_before_sync();
             mbar_arrive(&ctrl->p_ready[x]);
         }
+        uint32_t r[32];
         const bool have_o = ok && rhi[x] > rlo[x];
         if (have_o) {
             ok = mbar_wait(&ctrl->s_ready[x], s_phase, status, kErrSReady);  // last PV finished
