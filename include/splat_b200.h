@@ -32,6 +32,9 @@ extern "C" {
 
 #define SPLAT_B200_VERSION 100
 
+/* Capacity of the fixed intermediate buffer used by splat_attention_noalloc. */
+#define SPLAT_NOALLOC_SCRATCH_BYTES (64ll << 20)
+
 typedef enum {
     SPLAT_OK = 0,
     SPLAT_ERR_BAD_ARG = -1,          /* null pointer, negative size, inconsistent sizes        */
@@ -41,7 +44,8 @@ typedef enum {
     SPLAT_ERR_DEVICE_TIMEOUT = -5,   /* a bounded device-side wait gave up (see status words)   */
     SPLAT_ERR_UNSUPPORTED_SHAPE = -6,/* shape outside what the requested path implements        */
     SPLAT_ERR_DRIVER = -7,           /* tensor-map encoding / driver entry point failure        */
-    SPLAT_ERR_NO_DEVICE = -8
+    SPLAT_ERR_NO_DEVICE = -8,
+    SPLAT_ERR_SCRATCH_TOO_SMALL = -9 /* problem exceeds the fixed buffer of splat_attention_noalloc */
 } splat_status;
 
 typedef enum { SPLAT_F32 = 0, SPLAT_F16 = 1, SPLAT_BF16 = 2 } splat_dtype;
@@ -152,6 +156,23 @@ int32_t splat_attention_fused(const void* q, const void* k, int64_t k_stride_bh,
                               int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d, float scale,
                               int32_t dtype, int32_t path, const int32_t* plan_i32,
                               int32_t* status_word, void* stream);
+
+/* The three-launch chain (SDDMM, softmax in place, SpMM) for callers that cannot allocate device
+ * memory -- code running after its host application froze its memory pool, plug-ins that receive
+ * input/output buffers but own no allocator, callers that must avoid cudaMalloc's device-wide
+ * synchronisation.  The (bh, n_rows, trailing_dim) intermediate lives in a fixed 64 MiB array inside
+ * the library (held by every GPU that uses the library, until the process exits), so this entry
+ * point allocates nothing.  bh*n_rows*trailing_dim*sizeof(element) above
+ * SPLAT_NOALLOC_SCRATCH_BYTES returns SPLAT_ERR_SCRATCH_TOO_SMALL and launches nothing.  The first
+ * call on a device resolves the array's address there: make it before any stream capture.  All calls
+ * on a device share the array: calls that can overlap on the GPU race; the array keeps the last
+ * call's contents and nothing in it needs clearing.  Arguments as in splat_sddmm / splat_spmm.
+ * This entry point has no counterpart in the reference. */
+int32_t splat_attention_noalloc(const void* q, const void* k, int64_t k_stride_bh,
+                                int64_t k_stride_col, int64_t k_stride_k, const void* v, void* o,
+                                const float* sTod_lin, const float* sTod_tr, const float* nnzs,
+                                int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
+                                int64_t trailing_dim, float scale, int32_t dtype, void* stream);
 
 /* Tuning/debug switch, process-wide.  key 0: where the band kernel keeps the probability tile
  * between its two MMAs (1 = tensor memory, the default; 0 = shared memory).  No counterpart in

@@ -35,7 +35,7 @@ def test_version_and_status_strings():
     import splat_native as n
     assert n.version() == 100
     assert n.status_string(0) == "ok"
-    for code in range(-8, 0):
+    for code in range(-9, 0):
         assert n.status_string(code) not in ("ok", "unknown status")
     assert n.status_string(-99) == "unknown status"
 

@@ -1,0 +1,80 @@
+"""GPU: splat_attention_noalloc, the entry point for callers that cannot allocate device memory
+(host applications with a frozen memory pool, plug-ins that only receive input/output buffers,
+callers that must not trigger cudaMalloc's device-wide synchronisation).  It runs the same three
+kernels as splat_sddmm / splat_softmax / splat_spmm but keeps the (BH, L, trailing_dim) intermediate
+in a fixed 64 MiB array inside the library.
+
+Checked here, through the C ABI: its output equals the three existing entry points' output (same
+kernels, so bit for bit) on two calls in a row of different shape -- the second call finds the
+first call's leftovers in the shared array -- and a problem larger than the array is refused
+without a launch.  This file sorts last on purpose so that a stop-at-first-failure run has already
+executed every other test."""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import acsr_oracle as ao
+
+pytestmark = pytest.mark.gpu
+
+
+def _three_entry_points(n, q, kt, v, acsr, scale):
+    """Reference result from the existing entry points with caller-owned S and P buffers."""
+    B, H, L, d = q.shape
+    T = acsr[5]
+    s = torch.empty((B, H, L, T), dtype=q.dtype, device=q.device)
+    p = torch.empty_like(s)
+    o = torch.empty_like(q)
+    n.sddmm(q, kt, s, acsr[2], acsr[3], acsr[4], T)
+    n.softmax(s, p, acsr[4], T, scale)
+    n.spmm(p, v, o, acsr[2], acsr[3], acsr[4], T)
+    return o
+
+
+def _noalloc(n, q, kt, v, acsr, scale):
+    B, H, L, d = q.shape
+    o = torch.full_like(q, float("nan"))
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = n._lib.splat_attention_noalloc(
+        q.data_ptr(), kt.data_ptr(), kt.stride(1), kt.stride(3), kt.stride(2), v.data_ptr(),
+        o.data_ptr(), acsr[2].data_ptr(), acsr[3].data_ptr(), acsr[4].data_ptr(), B * H, L,
+        kt.shape[3], d, acsr[5], ctypes.c_float(scale), n.dtype_code(q.dtype), stream)
+    assert rc == 0, n.status_string(rc)
+    return o
+
+
+def test_noalloc_matches_existing_entry_points_twice_in_a_row():
+    import acsr_helpers as ah
+    import splat_native as n
+    torch.manual_seed(21)
+    calls = [  # (pattern, dtype, B, H, d): the second problem is smaller and of another dtype
+        (ah.create_causal_windowed_mask(640, 200), torch.bfloat16, 2, 3, 64),
+        (ah.create_dilated_mask(300, 17, 3), torch.float32, 1, 2, 32),
+    ]
+    for mask, dtype, B, H, d in calls:
+        L = len(mask)
+        acsr = ah.create_acsr(mask, 16, 0)
+        q, k, v = (torch.randn(B, H, L, d, device="cuda").to(dtype) for _ in range(3))
+        kt = k.transpose(2, 3)
+        scale = d ** -0.5
+        expect = _three_entry_points(n, q, kt, v, acsr, scale)
+        got = _noalloc(n, q, kt, v, acsr, scale)
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all()
+        assert torch.equal(got, expect), f"max diff {(got.float() - expect.float()).abs().max().item()}"
+
+
+def test_noalloc_refuses_problems_beyond_its_fixed_buffer():
+    import acsr_helpers as ah
+    import splat_native as n
+    L, d = 4096, 64
+    acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 1023), 16, 0)   # trailing_dim 1024
+    bh = n.NOALLOC_SCRATCH_BYTES // (L * 1024 * 2) + 1                     # one head too many
+    dummy = torch.zeros(16, dtype=torch.bfloat16, device="cuda")           # never dereferenced
+    rc = n._lib.splat_attention_noalloc(
+        dummy.data_ptr(), dummy.data_ptr(), L * d, d, 1, dummy.data_ptr(), dummy.data_ptr(),
+        acsr[2].data_ptr(), acsr[3].data_ptr(), acsr[4].data_ptr(), bh, L, L, d, acsr[5],
+        ctypes.c_float(1.0), n.dtype_code(torch.bfloat16), torch.cuda.current_stream().cuda_stream)
+    assert rc == -9 and "64 MiB" in n.status_string(rc)
+    torch.cuda.synchronize()

@@ -38,6 +38,8 @@ SIGNATURES = {
     "splat_attention_fused": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                               _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
     "splat_debug_set_option": [_i32, _i32],
+    "splat_attention_noalloc": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                _i64, _i64, _i64, _f32, _i32, _vp],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(_lib, _name)
@@ -48,6 +50,7 @@ _lib.splat_status_string.restype = ctypes.c_char_p
 
 PATTERN_BLOCKED, PATTERN_WINDOWED, PATTERN_CAUSAL_WINDOWED, PATTERN_STRIDED, PATTERN_DILATED = range(5)
 PATH_AUTO, PATH_GENERIC, PATH_BAND = 0, 1, 2
+NOALLOC_SCRATCH_BYTES = 64 << 20     # SPLAT_NOALLOC_SCRATCH_BYTES in include/splat_b200.h
 DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 

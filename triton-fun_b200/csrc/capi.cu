@@ -28,6 +28,8 @@ extern "C" const char* splat_status_string(int32_t status) {
         case SPLAT_ERR_UNSUPPORTED_SHAPE: return "shape not supported by the requested path";
         case SPLAT_ERR_DRIVER: return "CUDA driver call failed (tensor map encode / entry point)";
         case SPLAT_ERR_NO_DEVICE: return "no CUDA device";
+        case SPLAT_ERR_SCRATCH_TOO_SMALL:
+            return "problem needs more than the fixed 64 MiB intermediate of splat_attention_noalloc";
         default: return "unknown status";
     }
 }
