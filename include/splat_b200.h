@@ -174,11 +174,6 @@ int32_t splat_attention_noalloc(const void* q, const void* k, int64_t k_stride_b
                                 int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                                 int64_t trailing_dim, float scale, int32_t dtype, void* stream);
 
-/* Tuning/debug switch, process-wide.  key 0: where the band kernel keeps the probability tile
- * between its two MMAs (1 = tensor memory, the default; 0 = shared memory).  No counterpart in
- * the reference. */
-int32_t splat_debug_set_option(int32_t key, int32_t value);
-
 #ifdef __cplusplus
 }
 #endif

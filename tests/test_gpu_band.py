@@ -1,5 +1,4 @@
-"""GPU: the TMA + tcgen05 band kernel (both placements of the probability tile) against the CPU
-oracle, over window / blocked / strided / dilated patterns, ragged sizes and both 16-bit dtypes."""
+"""GPU: the TMA + tcgen05 band kernel against the CPU oracle, over window / blocked / strided / dilated patterns, ragged sizes and both 16-bit dtypes."""
 import pytest
 import torch
 
@@ -24,7 +23,7 @@ PATTERNS = [
 ]
 
 
-def _run(kind, L, p0, p1, d, dtype, p_in_tmem, seed, BH=(1, 3), scale=None, spread=1.0):
+def _run(kind, L, p0, p1, d, dtype, seed, BH=(1, 3), scale=None, spread=1.0):
     import acsr_helpers as ah
     import splat_native as n
     torch.manual_seed(seed)
@@ -34,40 +33,33 @@ def _run(kind, L, p0, p1, d, dtype, p_in_tmem, seed, BH=(1, 3), scale=None, spre
     q, k, v = (torch.randn(B, H, L, d).mul_(spread).to(dtype) for _ in range(3))
     scale = d ** -0.5 if scale is None else scale
     out = torch.full((B, H, L, d), float("nan"), dtype=dtype, device="cuda")
-    n.debug_set_option(0, 1 if p_in_tmem else 0)
-    try:
-        n.attention_fused(q.cuda(), k.cuda().transpose(2, 3), v.cuda(), out, acsr[2], acsr[3], acsr[4],
-                          scale, n.PATH_BAND)
-        n.check_status_word(0)
-    finally:
-        n.debug_set_option(0, 1)
+    n.attention_fused(q.cuda(), k.cuda().transpose(2, 3), v.cuda(), out, acsr[2], acsr[3], acsr[4],
+                      scale, n.PATH_BAND)
+    n.check_status_word(0)
     ref = at.attention_acsr(q, k.transpose(2, 3), v, meta, meta["trailing_dim"], scale)
     return out, ref
 
 
-@pytest.mark.parametrize("p_in_tmem", [False, True])
 @pytest.mark.parametrize("d", [128, 64])
-def test_band_first_light(d, p_in_tmem):
+def test_band_first_light(d):
     """Smallest interesting case first: if this fails the rest is skipped by -x."""
-    out, ref = _run(ao.PATTERN_CAUSAL_WINDOWED, 256, 99, 0, d, torch.bfloat16, p_in_tmem, 1)
-    assert_close(out, ref, torch.bfloat16, f"first light d={d} tmem={p_in_tmem}")
+    out, ref = _run(ao.PATTERN_CAUSAL_WINDOWED, 256, 99, 0, d, torch.bfloat16, 1)
+    assert_close(out, ref, torch.bfloat16, f"first light d={d}")
 
 
-@pytest.mark.parametrize("p_in_tmem", [False, True])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("d", [128, 64])
-def test_band_patterns(d, dtype, p_in_tmem):
+def test_band_patterns(d, dtype):
     for i, (kind, L, p0, p1) in enumerate(PATTERNS):
-        out, ref = _run(kind, L, p0, p1, d, dtype, p_in_tmem, 100 + i)
-        assert_close(out, ref, dtype, f"pattern {(kind, L, p0, p1)} d={d} tmem={p_in_tmem}")
+        out, ref = _run(kind, L, p0, p1, d, dtype, 100 + i)
+        assert_close(out, ref, dtype, f"pattern {(kind, L, p0, p1)} d={d}")
 
 
 def test_band_unscaled_scores_need_the_running_max():
     """scale = 1 with d = 128 gives scores of sigma ~ 11: exercises the lazy rescale of O."""
-    for p_in_tmem in (False, True):
-        out, ref = _run(ao.PATTERN_CAUSAL_WINDOWED, 1024, 511, 0, 128, torch.bfloat16, p_in_tmem, 7,
-                        scale=1.0)
-        assert_close(out, ref, torch.bfloat16, f"unscaled tmem={p_in_tmem}")
+    for d in (128, 64):
+        out, ref = _run(ao.PATTERN_CAUSAL_WINDOWED, 1024, 511, 0, d, torch.bfloat16, 7, scale=1.0)
+        assert_close(out, ref, torch.bfloat16, f"unscaled d={d}")
 
 
 def test_band_matches_generic_kernel_and_is_deterministic():

@@ -48,7 +48,6 @@ def test_host_side_argument_errors_launch_nothing():
     assert lib.splat_sddmm(None, None, 0, 0, 0, None, None, None, None, 1, 1, 1, 1, 1, 0, None) == -1
     assert lib.splat_pattern_row_summary(99, 10, 1, 0, ctypes.c_void_p(16), None) == -1
     assert lib.splat_pattern_row_summary(0, 10, 0, 0, ctypes.c_void_p(16), None) == -1
-    assert lib.splat_debug_set_option(12345, 0) == -1
 
 
 def test_cpu_device_is_rejected():

@@ -37,7 +37,6 @@ SIGNATURES = {
     "splat_spmm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
     "splat_attention_fused": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                               _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
-    "splat_debug_set_option": [_i32, _i32],
     "splat_attention_noalloc": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                 _i64, _i64, _i64, _f32, _i32, _vp],
 }
@@ -282,7 +281,3 @@ def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.
             sw.data_ptr(), _stream(dev)), "splat_attention_fused")
     if os.environ.get("SPLAT_B200_DEBUG"):
         check_status_word(dev)
-
-
-def debug_set_option(key: int, value: int) -> None:
-    check(_lib.splat_debug_set_option(key, value), "splat_debug_set_option")

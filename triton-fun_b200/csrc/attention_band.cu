@@ -14,8 +14,8 @@
 // lane), 8 = TMA producer, 9 = MMA issuer and TMEM owner.  Per key tile n and Q tile X:
 //     S_X = Q_X K_n^T        tcgen05.mma, operands in shared memory (128B swizzle, K-major)
 //     P_X = exp2(S_X*c - m)   softmax warps: tcgen05.ld, band mask, running max with a lazy O
-//                             rescale, P written back over S in tensor memory (or to shared memory)
-//     O_X += P_X V_n          tcgen05.mma, A from tensor memory (or shared), B = V tile (MN-major)
+//                             rescale, P written back over S in tensor memory
+//     O_X += P_X V_n          tcgen05.mma, A from tensor memory, B = V tile (MN-major)
 // The MMA warp issues [PV_A(n), S_A(n+1)], [PV_B(n), S_B(n+1)] so one tile's MMAs overlap the other
 // tile's softmax.  Rows with exactly one non-zero are described by the metadata as column `start`
 // whatever their class, so they are excluded from the band and written as O[i] = V[start_i];
@@ -33,7 +33,9 @@ using namespace tc;
 
 constexpr int kTile = 128;          // rows per Q tile and keys per K/V tile
 constexpr int kSubBytes = kTile * 128;  // one 64-element (128-byte) column chunk of a tile
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;          // warps 10, 11 only complete the third warpgroup
+constexpr int kRegsSoftmax = 224;       // per-thread register budgets after the re-split below
+constexpr int kRegsOther = 48;
 constexpr int kTmaWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kTmemCols = 512;
@@ -43,7 +45,22 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain: P stays below 2^8 bet
 // status-word codes (which wait gave up)
 enum : int { kErrQ = 1, kErrKvFull = 2, kErrKvEmpty = 3, kErrSReady = 4, kErrPReady = 5 };
 
+// Optional device-side timeline (profiling builds only, -DSPLAT_BAND_TRACE): one CTA records
+// (tag, SM clock) pairs per role into a caller-supplied buffer.
+#ifdef SPLAT_BAND_TRACE
+#define SPLAT_TRACE(role, tag)                                                          \
+    do {                                                                                \
+        if (trace_on && lane == 0 && trace_n[role] < 1024)                              \
+            p.trace[(role) * 1024 + trace_n[role]++] = ((long long)(tag) << 48) | (clock64() & 0xffffffffffffLL); \
+    } while (0)
+#else
+#define SPLAT_TRACE(role, tag) do { } while (0)
+#endif
+
 struct Params {
+#ifdef SPLAT_BAND_TRACE
+    long long* trace;
+#endif
     const float* lin;
     const float* tr;
     const float* nnzs;
@@ -69,15 +86,13 @@ struct Control {
     int32_t red_hi[8];
 };
 
-template <int D, bool kPTmem> struct Layout {
+template <int D> struct Layout {
     static constexpr int kSub = D / 64;
     static constexpr int kTileBytes = kSub * kSubBytes;
-    static constexpr int kStages = (kPTmem || D == 64) ? 4 : 3;
-    static constexpr int kPBytes = 2 * kSubBytes;  // one 128 x 128 P tile of 16-bit values
+    static constexpr int kStages = 4;
     static constexpr int kQOff = 0;
     static constexpr int kRingOff = 2 * kTileBytes;
-    static constexpr int kPOff = kRingOff + kStages * kTileBytes;
-    static constexpr int kCtrlOff = kPOff + (kPTmem ? 0 : 2 * kPBytes);
+    static constexpr int kCtrlOff = kRingOff + kStages * kTileBytes;
     static constexpr int kSmemBytes = kCtrlOff + (int)sizeof(Control) + 1024;  // + alignment slack
 };
 
@@ -122,22 +137,26 @@ __device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) 
         if (clock64() - t0 > 200000000LL) break;
 }
 
-template <typename T, int D, bool kPTmem>
+template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
-    using L = Layout<D, kPTmem>;
+    using L = Layout<D>;
     constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* s_q = smem + L::kQOff;
     uint8_t* s_ring = smem + L::kRingOff;
-    uint8_t* s_p = smem + L::kPOff;
     Control* ctrl = reinterpret_cast<Control*>(smem + L::kCtrlOff);
     volatile int32_t* status = p.status;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SPLAT_BAND_TRACE
+    const bool trace_on = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 &&
+                          blockIdx.z == gridDim.z / 2;
+    int trace_n[4] = {0, 0, 0, 0};
+#endif
     const int pair = blockIdx.x, res = blockIdx.y;
     const int64_t bh = blockIdx.z;
     const int u0 = pair * 2 * kTile;
@@ -151,7 +170,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctrl->s_ready[i], 1);
-            mbar_init(&ctrl->p_ready[i], kTile);
+            mbar_init(&ctrl->p_ready[i], 4);    // one arrival per softmax warp
         }
         mbar_init(&ctrl->drain, 1);
         mbar_fence_init();
@@ -211,8 +230,11 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int n_hi = max(rhi[0], rhi[1]);
     auto in_range = [&](int x, int n) { return n >= rlo[x] && n < rhi[x]; };
 
+    // The register file is re-split per role below (setmaxnreg): the eight softmax warps keep a
+    // whole 128-column score row in registers, the producer / issuer warps need very little.
     if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (lane == 0 && n_hi > n_lo) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
@@ -251,11 +273,12 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (lane == 0 && n_hi > n_lo) {
             constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kTile, 0);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
-            const uint32_t q_addr = smem_u32(s_q), ring_addr = smem_u32(s_ring), p_addr = smem_u32(s_p);
+            const uint32_t q_addr = smem_u32(s_q), ring_addr = smem_u32(s_ring);
 
             auto issue_s = [&](int x, int stage) {
                 const uint32_t a_base = q_addr + x * L::kTileBytes;
@@ -274,13 +297,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int kk = 0; kk < kTile / 16; ++kk) {
                     const uint64_t b_desc = smem_desc_sw128(b_base + kk * 2048, kSubBytes, 1024);
                     const uint32_t accumulate = (acc || kk > 0) ? 1u : 0u;
-                    if constexpr (kPTmem) {
-                        mma_ts(d_tmem, tmem_base + x * kTile + kk * 8, b_desc, idesc_pv, accumulate);
-                    } else {
-                        const uint32_t off = (kk >> 2) * kSubBytes + (kk & 3) * 32;
-                        mma_ss(d_tmem, smem_desc_sw128(p_addr + x * L::kPBytes + off, 16, 1024),
-                               b_desc, idesc_pv, accumulate);
-                    }
+                    mma_ts(d_tmem, tmem_base + x * kTile + kk * 8, b_desc, idesc_pv, accumulate);
                 }
             };
             auto full_wait = [&](int item) {
@@ -310,13 +327,16 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int x = 0; x < 2 && ok; ++x) {
                     const bool cur = in_range(x, n), nxt = has_next && in_range(x, n + 1);
                     if (cur) {
+                        SPLAT_TRACE(2, 10 + x);
                         ok = mbar_wait(&ctrl->p_ready[x], p_phase[x], status, kErrPReady);
                         if (!ok) break;
                         p_phase[x] ^= 1u;
                         tc_fence_after_sync();
+                        SPLAT_TRACE(2, 12 + x);
                         issue_pv(x, item_v % kStages, n > rlo[x]);
                     }
                     if (nxt) issue_s(x, item_k % kStages);
+                    SPLAT_TRACE(2, 14 + x);
                     // next scores ready -- or, after the last PV of this tile, its output final
                     if (cur || nxt) mma_commit(&ctrl->s_ready[x]);
                 }
@@ -330,8 +350,9 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 mbar_wait_quiet(&ctrl->drain, 0);
             }
         }
-    } else {
+    } else if (warp < 8) {
         // ------------------------------------------------------------------ softmax + epilogue
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         const int x = warp >> 2;
         const int t = (warp & 3) * 32 + lane;  // row in tile == TMEM lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
@@ -342,11 +363,13 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         bool ok = true;
         const float sc = p.scale_log2;
         for (int n = rlo[x]; n < rhi[x]; ++n) {
+            if ((warp & 3) == 0) SPLAT_TRACE(x, 1);
             ok = mbar_wait(&ctrl->s_ready[x], s_phase, status, kErrSReady);
             ok = __all_sync(0xffffffffu, ok);  // keep the warp together for the aligned tcgen05 ops
             if (!ok) break;
             s_phase ^= 1u;
             tc_fence_after_sync();
+            if ((warp & 3) == 0) SPLAT_TRACE(x, 2);
             const int c0 = n * kTile;
             const int v_lo = my_a - c0;               // valid columns of this tile: [v_lo, v_hi)
             const int v_hi = my_n > 0 ? my_a + my_n - c0 : INT_MIN;
@@ -357,6 +380,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_addr + ch * 32, r + ch * 32);
             tmem_ld_wait();
+            if ((warp & 3) == 0) SPLAT_TRACE(x, 3);
             if (!warp_full) {   // band edge: columns outside [v_lo, v_hi) become -inf (exp2 -> 0)
 #pragma unroll
                 for (int j = 0; j < kTile; ++j)
@@ -371,6 +395,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     mx[c] = fmax3(mx[c], __uint_as_float(r[j + 2 * c]), __uint_as_float(r[j + 2 * c + 1]));
             }
             const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            if ((warp & 3) == 0) SPLAT_TRACE(x, 4);
             const float m_new = fmaxf(m_used, mt * sc);
             const bool need = (m_new - m_used) > kRescaleThreshold;  // false when both are -inf
             const float corr = need ? ex2(m_used - m_new) : 1.f;
@@ -392,18 +417,9 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 r[(j >> 1) + 1] = pack2<T>(a1.x, a1.y);
             }
             l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
-            if constexpr (kPTmem) {
-                tmem_st32(s_addr, r);            // P (64 packed columns) over the first half of S
-                tmem_st32(s_addr + 32, r + 32);
-            } else {
-                // K-major, 128-byte rows, 16-byte chunk index XOR (row mod 8)
-#pragma unroll
-                for (int cc16 = 0; cc16 < 16; ++cc16) {
-                    uint8_t* prow = s_p + x * L::kPBytes + (cc16 >> 3) * kSubBytes + t * 128;
-                    *reinterpret_cast<uint4*>(prow + (((cc16 & 7) ^ (t & 7)) << 4)) =
-                        make_uint4(r[cc16 * 4], r[cc16 * 4 + 1], r[cc16 * 4 + 2], r[cc16 * 4 + 3]);
-                }
-            }
+            if ((warp & 3) == 0) SPLAT_TRACE(x, 5);
+            tmem_st32(s_addr, r);            // P (64 packed columns) over the first half of S
+            tmem_st32(s_addr + 32, r + 32);
             // lazy rescale of the accumulator (rare): only when some row's maximum moved by > 2^8
             if (__any_sync(0xffffffffu, need) && n > rlo[x]) {
                 uint32_t o[32];
@@ -416,10 +432,11 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tmem_st32(o_addr + ch * 32, o);
                 }
             }
-            if constexpr (kPTmem) tmem_st_wait();
-            else { tmem_st_wait(); fence_proxy_async_smem(); }
+            tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive(&ctrl->p_ready[x]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctrl->p_ready[x]);
+            if ((warp & 3) == 0) SPLAT_TRACE(x, 6);
         }
         uint32_t r[32];
         const bool have_o = ok && rhi[x] > rlo[x];
@@ -457,6 +474,9 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             for (int q4 = 0; q4 < 4; ++q4)
                 *reinterpret_cast<uint4*>(orow + ch * 32 + q4 * 8) = out[q4];
         }
+    } else {
+        // warps 10, 11: idle members of the third warpgroup
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     }
 
     tc_fence_before_sync();
@@ -507,13 +527,15 @@ static bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t 
     return rc == CUDA_SUCCESS;
 }
 
-static int g_p_in_tmem = 1;
+#ifdef SPLAT_BAND_TRACE
+static long long* g_trace = nullptr;
+#endif
 
-template <typename T, int D, bool kPTmem>
+template <typename T, int D>
 static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                       const Params& prm, int64_t bh, cudaStream_t st) {
-    using L = Layout<D, kPTmem>;
-    auto kern = attention_band_kernel<T, D, kPTmem>;
+    using L = Layout<D>;
+    auto kern = attention_band_kernel<T, D>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) !=
         cudaSuccess)
         return SPLAT_ERR_LAUNCH;
@@ -526,11 +548,7 @@ static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 template <typename T>
 static int32_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const Params& prm, int64_t bh, int64_t d, cudaStream_t st) {
-    if (d == 128)
-        return g_p_in_tmem ? launch<T, 128, true>(mq, mk, mv, prm, bh, st)
-                           : launch<T, 128, false>(mq, mk, mv, prm, bh, st);
-    return g_p_in_tmem ? launch<T, 64, true>(mq, mk, mv, prm, bh, st)
-                       : launch<T, 64, false>(mq, mk, mv, prm, bh, st);
+    return d == 128 ? launch<T, 128>(mq, mk, mv, prm, bh, st) : launch<T, 64>(mq, mk, mv, prm, bh, st);
 }
 
 }  // namespace band
@@ -565,14 +583,17 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.o = o; prm.status = status_word;
     prm.n_rows = n_rows; prm.rows_v = (int)(n_rows / stride); prm.stride = (int)stride;
     prm.scale_log2 = scale * kLog2e;
+#ifdef SPLAT_BAND_TRACE
+    prm.trace = band::g_trace;
+#endif
     if (dtype == SPLAT_BF16) return band::launch_d<__nv_bfloat16>(mq, mk, mv, prm, bh, d, st);
     return band::launch_d<__half>(mq, mk, mv, prm, bh, d, st);
 }
 
 }  // namespace splat
 
-// Debug/tuning switch: key 0 = where the band kernel keeps P (1 tensor memory, 0 shared memory).
-extern "C" int32_t splat_debug_set_option(int32_t key, int32_t value) {
-    if (key == 0) { splat::band::g_p_in_tmem = value ? 1 : 0; return SPLAT_OK; }
-    return SPLAT_ERR_BAD_ARG;
+#ifdef SPLAT_BAND_TRACE
+extern "C" void splat_debug_set_trace(void* device_buffer_4x1024_i64) {
+    splat::band::g_trace = reinterpret_cast<long long*>(device_buffer_4x1024_i64);
 }
+#endif
