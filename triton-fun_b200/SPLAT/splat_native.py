@@ -12,7 +12,7 @@ import os
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG_DIR, "libsplat_b200.so")
+LIB_PATH = os.environ.get("SPLAT_B200_LIB") or os.path.join(_PKG_DIR, "libsplat_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

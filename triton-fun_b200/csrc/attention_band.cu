@@ -9,17 +9,22 @@
 // (d, s, L/s, BH) of the (BH, L, d) array: box (64, 1, 128, 1) at (chunk, r, u0, bh).
 // s = 1 is the plain sliding-window case.
 //
-// One CTA owns two 128-row Q tiles (A, B) of one (bh, r) and walks the union of their key ranges in
-// 128-key steps.  Warps: 0-3 softmax/epilogue for tile A, 4-7 for tile B (thread = row = TMEM
-// lane), 8 = TMA producer, 9 = MMA issuer and TMEM owner.  Per key tile n and Q tile X:
-//     S_X = Q_X K_n^T        tcgen05.mma, operands in shared memory (128B swizzle, K-major)
-//     P_X = exp2(S_X*c - m)   softmax warps: tcgen05.ld, band mask, running max with a lazy O
-//                             rescale, P written back over S in tensor memory
-//     O_X += P_X V_n          tcgen05.mma, A from tensor memory, B = V tile (MN-major)
-// The MMA warp issues [PV_A(n), S_A(n+1)], [PV_B(n), S_B(n+1)] so one tile's MMAs overlap the other
-// tile's softmax.  Rows with exactly one non-zero are described by the metadata as column `start`
-// whatever their class, so they are excluded from the band and written as O[i] = V[start_i];
-// rows with no non-zero are written as zero.
+// One CTA owns two 128-row Q tiles (A, B) of one (bh, r).  K/V travel through a shared-memory ring
+// in 128-key tiles (TMA, 128-byte swizzle); the math advances in 64-key steps k so that the 128
+// score columns a Q tile owns in tensor memory form TWO buffers:
+//     S_X(k)  = Q_X K(k)^T     tcgen05.mma 128x64x16, operands in shared memory, into buffer k mod 2
+//     P_X(k)  = exp2(S c - m)   softmax warps: tcgen05.ld the 64 scores of their row, band mask,
+//                               running max with a lazy rescale of O, exp2 with the scale folded
+//                               in, 16-bit P stored over the consumed scores of the same buffer
+//     O_X    += P_X(k) V(k)     tcgen05.mma 128xdx16, A = P from tensor memory, B = V rows (MN-major)
+// While the softmax warps work on buffer k mod 2 the tensor core already fills the other buffer
+// with S_X(k+1), so neither side waits for the other in steady state: per Q tile the issue order is
+// S(k0), S(k0+1), then for every k: PV(k), S(k+2).
+// Warps: 0-3 softmax/epilogue of tile A, 4-7 of tile B (thread = row = TMEM lane), 8 = TMA producer,
+// 9 / 10 = MMA issuers of tile A / B (9 also owns tensor memory), 11 idle.
+// Rows with exactly one non-zero are described by the metadata as column `start` whatever their
+// class, so they are excluded from the band and written as O[i] = V[start_i]; rows with no
+// non-zero are written as zero.
 #include <limits.h>
 #include <type_traits>
 
@@ -31,15 +36,14 @@ namespace band {
 
 using namespace tc;
 
-constexpr int kTile = 128;          // rows per Q tile and keys per K/V tile
+constexpr int kTile = 128;              // rows per Q tile and keys per K/V ring tile
+constexpr int kStep = 64;               // keys per math step (one score buffer)
 constexpr int kSubBytes = kTile * 128;  // one 64-element (128-byte) column chunk of a tile
-constexpr int kThreads = 384;          // warps 10, 11 only complete the third warpgroup
-constexpr int kRegsSoftmax = 224;       // per-thread register budgets after the re-split below
-constexpr int kRegsOther = 48;
+constexpr int kThreads = 384;
 constexpr int kTmaWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kMmaWarp = 9;             // 9: tile A (+ TMEM alloc), 10: tile B
 constexpr int kTmemCols = 512;
-constexpr int kMaxStages = 4;
+constexpr int kStages = 4;              // K/V ring, one 128-key tile per stage
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain: P stays below 2^8 between rescales
 
 // status-word codes (which wait gave up)
@@ -75,11 +79,11 @@ struct Params {
 
 struct Control {
     uint64_t q_full;
-    uint64_t kv_full[kMaxStages];
-    uint64_t kv_empty[kMaxStages];
-    uint64_t s_ready[2];
-    uint64_t p_ready[2];
-    uint64_t drain;
+    uint64_t kv_full[kStages];
+    uint64_t kv_empty[kStages];  // two arrivals: both MMA issuers release every ring tile
+    uint64_t s_ready[2][2];      // [Q tile][buffer] MMA -> softmax: scores ready / previous PV done
+    uint64_t p_ready[2][2];      // [Q tile][buffer] softmax -> MMA: P stored (4 warp arrivals)
+    uint64_t drain[2];
     uint32_t tmem_base;
     int32_t abort_at_entry;
     int32_t red_lo[8];
@@ -89,7 +93,6 @@ struct Control {
 template <int D> struct Layout {
     static constexpr int kSub = D / 64;
     static constexpr int kTileBytes = kSub * kSubBytes;
-    static constexpr int kStages = 4;
     static constexpr int kQOff = 0;
     static constexpr int kRingOff = 2 * kTileBytes;
     static constexpr int kCtrlOff = kRingOff + kStages * kTileBytes;
@@ -101,7 +104,6 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -142,7 +144,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
     using L = Layout<D>;
-    constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -164,15 +165,17 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (threadIdx.x == 0) {
         ctrl->abort_at_entry = *status;
         mbar_init(&ctrl->q_full, 1);
-        for (int i = 0; i < kMaxStages; ++i) {
+        for (int i = 0; i < kStages; ++i) {
             mbar_init(&ctrl->kv_full[i], 1);
-            mbar_init(&ctrl->kv_empty[i], 1);
+            mbar_init(&ctrl->kv_empty[i], 2);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&ctrl->s_ready[i], 1);
-            mbar_init(&ctrl->p_ready[i], 4);    // one arrival per softmax warp
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&ctrl->s_ready[i][b], 1);
+                mbar_init(&ctrl->p_ready[i][b], 4);  // one arrival per softmax warp
+            }
+            mbar_init(&ctrl->drain[i], 1);
         }
-        mbar_init(&ctrl->drain, 1);
         mbar_fence_init();
     }
 
@@ -191,8 +194,8 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             if (ra.nnz > 1) {
                 my_a = (ra.start - res) / p.stride;
                 my_n = ra.nnz;
-                lo = my_a / kTile;
-                hi = (my_a + my_n + kTile - 1) / kTile;
+                lo = my_a / kStep;
+                hi = (my_a + my_n + kStep - 1) / kStep;
             }
         }
         lo = warp_min_i(lo);
@@ -211,9 +214,9 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    // Key-tile ranges [lo, hi) of the two Q tiles and their union.
-    int rlo[2], rhi[2];
-    const int max_tiles = (p.rows_v + kTile - 1) / kTile;
+    // Step ranges [klo, khi) (64-key units) of the two Q tiles and the ring-tile range of their union.
+    int klo[2], khi[2];
+    const int max_steps = (p.rows_v + kStep - 1) / kStep;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         int lo = INT_MAX, hi = 0;
@@ -221,21 +224,20 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             lo = min(lo, ctrl->red_lo[x * 4 + w]);
             hi = max(hi, ctrl->red_hi[x * 4 + w]);
         }
-        hi = min(hi, max_tiles);
+        hi = min(hi, max_steps);
         if (lo >= hi) { lo = 0; hi = 0; }
-        rlo[x] = lo; rhi[x] = hi;
+        klo[x] = lo; khi[x] = hi;
     }
-    const bool has_a = rhi[0] > rlo[0], has_b = rhi[1] > rlo[1];
-    const int n_lo = has_a ? (has_b ? min(rlo[0], rlo[1]) : rlo[0]) : rlo[1];
-    const int n_hi = max(rhi[0], rhi[1]);
-    auto in_range = [&](int x, int n) { return n >= rlo[x] && n < rhi[x]; };
+    const bool has_a = khi[0] > klo[0], has_b = khi[1] > klo[1];
+    const int k_min = has_a ? (has_b ? min(klo[0], klo[1]) : klo[0]) : klo[1];
+    const int k_max = max(khi[0], khi[1]);
+    const int n_lo = k_min >> 1, n_hi = (k_max + 1) >> 1;   // 128-key ring tiles [n_lo, n_hi)
+    const bool any_work = k_max > k_min;
 
-    // The register file is re-split per role below (setmaxnreg): the eight softmax warps keep a
-    // whole 128-column score row in registers, the producer / issuer warps need very little.
     if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (lane == 0 && n_hi > n_lo) {
+        // Ring items in order K(n_lo), V(n_lo), K(n_lo+1), V(n_lo+1), ...
+        if (lane == 0 && any_work) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
@@ -271,157 +273,182 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     mbar_wait_quiet(&ctrl->kv_full[i % kStages], (uint32_t)(i / kStages) & 1u);
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (lane == 0 && n_hi > n_lo) {
-            constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kTile, 0);
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+        // ------------------------------------------------------------------ MMA issuer of tile x
+        // Uses ring item 2(n - n_lo) = K tile n and 2(n - n_lo) + 1 = V tile n; every item is
+        // waited for and released exactly once by each issuer, used or not.
+        const int x = warp - kMmaWarp;
+        if (lane == 0 && any_work) {
+            constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, 0);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
-            const uint32_t q_addr = smem_u32(s_q), ring_addr = smem_u32(s_ring);
+            const uint32_t ring_addr = smem_u32(s_ring);
+            const uint32_t q_base = smem_u32(s_q) + x * L::kTileBytes;
+            const uint32_t s_tmem = tmem_base + x * kTile;
+            const uint32_t o_tmem = tmem_base + 2 * kTile + x * D;
+            const int lo = klo[x], hi = khi[x];
+            bool ok = true;
 
-            auto issue_s = [&](int x, int stage) {
-                const uint32_t a_base = q_addr + x * L::kTileBytes;
-                const uint32_t b_base = ring_addr + stage * L::kTileBytes;
+            auto stage_of = [&](int item) { return item % kStages; };
+            auto full_wait = [&](int item) {
+                return mbar_wait(&ctrl->kv_full[stage_of(item)], (uint32_t)(item / kStages) & 1u,
+                                 status, kErrKvFull);
+            };
+            auto release = [&](int item) { mma_commit(&ctrl->kv_empty[stage_of(item)]); };
+            // S(k): 64 keys = rows [64(k&1), +64) of K tile k/2, into score buffer k&1
+            auto issue_s = [&](int k) {
+                const uint32_t b_base = ring_addr + stage_of(2 * ((k >> 1) - n_lo)) * L::kTileBytes +
+                                        (k & 1) * (kStep * 128);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kSubBytes + (kk & 3) * 32;
-                    mma_ss(tmem_base + x * kTile, smem_desc_sw128(a_base + off, 16, 1024),
+                    mma_ss(s_tmem + (k & 1) * kStep, smem_desc_sw128(q_base + off, 16, 1024),
                            smem_desc_sw128(b_base + off, 16, 1024), idesc_qk, kk > 0);
                 }
             };
-            auto issue_pv = [&](int x, int stage, bool acc) {
-                const uint32_t d_tmem = tmem_base + 2 * kTile + x * D;
-                const uint32_t b_base = ring_addr + stage * L::kTileBytes;
+            // O += P(k) V(k): P packed in the first 32 columns of buffer k&1, V rows [64(k&1), +64)
+            auto issue_pv = [&](int k, bool acc) {
+                const uint32_t b_base = ring_addr + stage_of(2 * ((k >> 1) - n_lo) + 1) * L::kTileBytes +
+                                        (k & 1) * (kStep * 128);
 #pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk) {
-                    const uint64_t b_desc = smem_desc_sw128(b_base + kk * 2048, kSubBytes, 1024);
-                    const uint32_t accumulate = (acc || kk > 0) ? 1u : 0u;
-                    mma_ts(d_tmem, tmem_base + x * kTile + kk * 8, b_desc, idesc_pv, accumulate);
-                }
+                for (int kk = 0; kk < kStep / 16; ++kk)
+                    mma_ts(o_tmem, s_tmem + (k & 1) * kStep + kk * 8,
+                           smem_desc_sw128(b_base + kk * 2048, kSubBytes, 1024), idesc_pv,
+                           (acc || kk > 0) ? 1u : 0u);
             };
-            auto full_wait = [&](int item) {
-                return mbar_wait(&ctrl->kv_full[item % kStages], (uint32_t)(item / kStages) & 1u,
-                                 status, kErrKvFull);
-            };
+            // last step of tile x that reads ring tile n
+            auto last_user = [&](int k) { return (k & 1) == 1 || k == hi - 1; };
 
-            bool ok = mbar_wait(&ctrl->q_full, 0, status, kErrQ);
-            uint32_t p_phase[2] = {0, 0};
-            ok = ok && full_wait(0);
-            if (ok) {
-                tc_fence_after_sync();
-                for (int x = 0; x < 2; ++x)
-                    if (in_range(x, n_lo)) {
-                        issue_s(x, 0);
-                        mma_commit(&ctrl->s_ready[x]);
+            ok = mbar_wait(&ctrl->q_full, 0, status, kErrQ);
+            if (hi > lo) {
+                const int t_lo = lo >> 1, t_hi = (hi + 1) >> 1;   // ring tiles tile x reads
+                // tiles before the range: pass them on untouched
+                for (int n = n_lo; n < t_lo && ok; ++n)
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        ok = full_wait(2 * (n - n_lo) + w);
+                        if (ok) release(2 * (n - n_lo) + w);
                     }
-                mma_commit(&ctrl->kv_empty[0]);
-            }
-            for (int n = n_lo; n < n_hi && ok; ++n) {
-                const int item_v = 2 * (n - n_lo) + 1, item_k = item_v + 1;
-                const bool has_next = n + 1 < n_hi;
-                ok = full_wait(item_v);
-                if (ok && has_next) ok = full_wait(item_k);
-                if (!ok) break;
-                tc_fence_after_sync();
-                for (int x = 0; x < 2 && ok; ++x) {
-                    const bool cur = in_range(x, n), nxt = has_next && in_range(x, n + 1);
-                    if (cur) {
-                        SPLAT_TRACE(2, 10 + x);
-                        ok = mbar_wait(&ctrl->p_ready[x], p_phase[x], status, kErrPReady);
-                        if (!ok) break;
-                        p_phase[x] ^= 1u;
-                        tc_fence_after_sync();
-                        SPLAT_TRACE(2, 12 + x);
-                        issue_pv(x, item_v % kStages, n > rlo[x]);
-                    }
-                    if (nxt) issue_s(x, item_k % kStages);
-                    SPLAT_TRACE(2, 14 + x);
-                    // next scores ready -- or, after the last PV of this tile, its output final
-                    if (cur || nxt) mma_commit(&ctrl->s_ready[x]);
+                // first two score buffers
+                for (int k = lo; k < min(lo + 2, hi) && ok; ++k) {
+                    const int item_k = 2 * ((k >> 1) - n_lo);
+                    if (k == lo || (k & 1) == 0) ok = full_wait(item_k);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_s(k);
+                    mma_commit(&ctrl->s_ready[x][k & 1]);
+                    if (last_user(k)) release(item_k);
                 }
-                if (!ok) break;
-                mma_commit(&ctrl->kv_empty[item_v % kStages]);
-                if (has_next) mma_commit(&ctrl->kv_empty[item_k % kStages]);
+                uint32_t p_phase[2] = {0, 0};
+                for (int k = lo; k < hi && ok; ++k) {
+                    const int item_v = 2 * ((k >> 1) - n_lo) + 1;
+                    if (k == lo || (k & 1) == 0) ok = full_wait(item_v);
+                    if (!ok) break;
+                    SPLAT_TRACE(2 + x, 10);
+                    ok = mbar_wait(&ctrl->p_ready[x][k & 1], p_phase[k & 1], status, kErrPReady);
+                    if (!ok) break;
+                    p_phase[k & 1] ^= 1u;
+                    tc_fence_after_sync();
+                    SPLAT_TRACE(2 + x, 11);
+                    issue_pv(k, k > lo);
+                    if (last_user(k)) release(item_v);
+                    if (k + 2 < hi) {
+                        const int item_k = 2 * (((k + 2) >> 1) - n_lo);
+                        if (((k + 2) & 1) == 0) ok = full_wait(item_k);   // first reader of that K tile
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_s(k + 2);
+                        if (last_user(k + 2)) release(item_k);
+                    }
+                    // buffer k&1: next scores ready -- and, in any case, PV(k) complete
+                    mma_commit(&ctrl->s_ready[x][k & 1]);
+                    SPLAT_TRACE(2 + x, 12);
+                }
+                // tiles after the range
+                for (int n = t_hi; n < n_hi && ok; ++n)
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        ok = full_wait(2 * (n - n_lo) + w);
+                        if (ok) release(2 * (n - n_lo) + w);
+                    }
+            } else {
+                for (int item = 0; item < 2 * (n_hi - n_lo) && ok; ++item) {
+                    ok = full_wait(item);
+                    if (ok) release(item);
+                }
             }
             if (!ok) {
                 // let the tensor pipe drain before tensor memory is released
-                mma_commit(&ctrl->drain);
-                mbar_wait_quiet(&ctrl->drain, 0);
+                mma_commit(&ctrl->drain[x]);
+                mbar_wait_quiet(&ctrl->drain[x], 0);
             }
         }
     } else if (warp < 8) {
         // ------------------------------------------------------------------ softmax + epilogue
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         const int x = warp >> 2;
-        const int t = (warp & 3) * 32 + lane;  // row in tile == TMEM lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_addr + x * kTile;
         const uint32_t o_addr = lane_addr + 2 * kTile + x * D;
         float m_used = -INFINITY, l_sum = 0.f;
-        uint32_t s_phase = 0;
+        uint32_t s_phase[2] = {0, 0};
+        bool pv_waited = false;   // the "PV(k-1) done" phase of the other buffer was consumed early
         bool ok = true;
         const float sc = p.scale_log2;
-        for (int n = rlo[x]; n < rhi[x]; ++n) {
-            if ((warp & 3) == 0) SPLAT_TRACE(x, 1);
-            ok = mbar_wait(&ctrl->s_ready[x], s_phase, status, kErrSReady);
-            ok = __all_sync(0xffffffffu, ok);  // keep the warp together for the aligned tcgen05 ops
-            if (!ok) break;
-            s_phase ^= 1u;
+        const float2 sc2 = make_float2(sc, sc);
+        const bool tr = (warp & 3) == 0;
+        (void)tr;
+        for (int k = klo[x]; k < khi[x]; ++k) {
+            const int b = k & 1;
+            if (tr) SPLAT_TRACE(x, 1);
+            if (!pv_waited) {
+                ok = mbar_wait(&ctrl->s_ready[x][b], s_phase[b], status, kErrSReady);
+                ok = __all_sync(0xffffffffu, ok);  // keep the warp together for the aligned tcgen05 ops
+                if (!ok) break;
+                s_phase[b] ^= 1u;
+            }
+            pv_waited = false;
             tc_fence_after_sync();
-            if ((warp & 3) == 0) SPLAT_TRACE(x, 2);
-            const int c0 = n * kTile;
-            const int v_lo = my_a - c0;               // valid columns of this tile: [v_lo, v_hi)
+            if (tr) SPLAT_TRACE(x, 2);
+            const int c0 = k * kStep;
+            const int v_lo = my_a - c0;               // valid columns of this step: [v_lo, v_hi)
             const int v_hi = my_n > 0 ? my_a + my_n - c0 : INT_MIN;
-            const bool warp_full = __all_sync(0xffffffffu, v_lo <= 0 && v_hi >= kTile);
+            const bool edge = !__all_sync(0xffffffffu, v_lo <= 0 && v_hi >= kStep);
 
-            // the whole score row of this thread, one wait for the four loads
-            uint32_t r[kTile];
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_addr + ch * 32, r + ch * 32);
+            uint32_t r[kStep];
+            tmem_ld32(s_addr + b * kStep, r);
+            tmem_ld32(s_addr + b * kStep + 32, r + 32);
             tmem_ld_wait();
-            if ((warp & 3) == 0) SPLAT_TRACE(x, 3);
-            if (!warp_full) {   // band edge: columns outside [v_lo, v_hi) become -inf (exp2 -> 0)
+            if (tr) SPLAT_TRACE(x, 3);
+            if (edge) {   // band edge: columns outside [v_lo, v_hi) become -inf (exp2 -> 0)
 #pragma unroll
-                for (int j = 0; j < kTile; ++j)
+                for (int j = 0; j < kStep; ++j)
                     r[j] = (j >= v_lo && j < v_hi) ? r[j] : 0xff800000u;
             }
             // row maximum, four independent chains of 3-input max
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < kTile; j += 8) {
+            for (int j = 0; j < kStep; j += 8) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
                     mx[c] = fmax3(mx[c], __uint_as_float(r[j + 2 * c]), __uint_as_float(r[j + 2 * c + 1]));
             }
             const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            if ((warp & 3) == 0) SPLAT_TRACE(x, 4);
             const float m_new = fmaxf(m_used, mt * sc);
             const bool need = (m_new - m_used) > kRescaleThreshold;  // false when both are -inf
             const float corr = need ? ex2(m_used - m_new) : 1.f;
             if (need) m_used = m_new;
             l_sum *= corr;
             const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+            if (tr) SPLAT_TRACE(x, 4);
 
-            // probabilities: exp2(s*c - m) with packed fp32x2 FMAs, row sum, 16-bit pack in place
-            const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-m_eff, -m_eff);
-            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < kTile; j += 4) {
-                float2 a0 = fma2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc2, nm2);
-                float2 a1 = fma2(make_float2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), sc2, nm2);
-                a0.x = ex2(a0.x); a0.y = ex2(a0.y); a1.x = ex2(a1.x); a1.y = ex2(a1.y);
-                acc0 = add2(acc0, a0);
-                acc1 = add2(acc1, a1);
-                r[j >> 1] = pack2<T>(a0.x, a0.y);
-                r[(j >> 1) + 1] = pack2<T>(a1.x, a1.y);
-            }
-            l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
-            if ((warp & 3) == 0) SPLAT_TRACE(x, 5);
-            tmem_st32(s_addr, r);            // P (64 packed columns) over the first half of S
-            tmem_st32(s_addr + 32, r + 32);
-            // lazy rescale of the accumulator (rare): only when some row's maximum moved by > 2^8
-            if (__any_sync(0xffffffffu, need) && n > rlo[x]) {
+            // lazy rescale of the accumulator (rare): some row's maximum moved by more than 2^8.
+            // PV(k-1) may still be running: its completion is the next arrival on the OTHER
+            // buffer's barrier, which is consumed here instead of at the top of step k+1.
+            if (k > klo[x] && __any_sync(0xffffffffu, need)) {
+                ok = mbar_wait(&ctrl->s_ready[x][b ^ 1], s_phase[b ^ 1], status, kErrSReady);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                s_phase[b ^ 1] ^= 1u;
+                pv_waited = true;
+                tc_fence_after_sync();
                 uint32_t o[32];
 #pragma unroll
                 for (int ch = 0; ch < D / 32; ++ch) {
@@ -432,20 +459,43 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tmem_st32(o_addr + ch * 32, o);
                 }
             }
+
+            // probabilities: exp2(s*c - m) with packed fp32x2 FMAs, row sum, 16-bit pack in place
+            const float2 nm2 = make_float2(-m_eff, -m_eff);
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kStep; j += 4) {
+                float2 a0 = fma2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc2, nm2);
+                float2 a1 = fma2(make_float2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), sc2, nm2);
+                a0.x = ex2(a0.x); a0.y = ex2(a0.y); a1.x = ex2(a1.x); a1.y = ex2(a1.y);
+                acc0 = add2(acc0, a0);
+                acc1 = add2(acc1, a1);
+                r[j >> 1] = pack2<T>(a0.x, a0.y);
+                r[(j >> 1) + 1] = pack2<T>(a1.x, a1.y);
+            }
+            l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+            tmem_st32(s_addr + b * kStep, r);   // P: 32 packed columns over the consumed scores
+            if (tr) SPLAT_TRACE(x, 5);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ctrl->p_ready[x]);
-            if ((warp & 3) == 0) SPLAT_TRACE(x, 6);
+            if (lane == 0) mbar_arrive(&ctrl->p_ready[x][b]);
+            if (tr) SPLAT_TRACE(x, 6);
         }
-        uint32_t r[32];
-        const bool have_o = ok && rhi[x] > rlo[x];
+        const int steps = khi[x] - klo[x];
+        const bool have_o = ok && steps > 0;
         if (have_o) {
-            ok = mbar_wait(&ctrl->s_ready[x], s_phase, status, kErrSReady);  // last PV finished
-            ok = __all_sync(0xffffffffu, ok);
+            // the last PV on each buffer that was used
+            for (int i = min(steps, 2); i >= 1 && ok; --i) {
+                const int b = (khi[x] - i) & 1;
+                if (pv_waited && i == 2) continue;   // already consumed by a late rescale
+                ok = mbar_wait(&ctrl->s_ready[x][b], s_phase[b], status, kErrSReady);
+                ok = __all_sync(0xffffffffu, ok);
+            }
             tc_fence_after_sync();
         }
         // epilogue: O / l for band rows, V[start] for single-element rows, zero otherwise
+        uint32_t r[32];
         T* orow = row_real >= 0 ? reinterpret_cast<T*>(p.o) + (bh * p.n_rows + row_real) * D : nullptr;
         const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
@@ -474,9 +524,6 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             for (int q4 = 0; q4 < 4; ++q4)
                 *reinterpret_cast<uint4*>(orow + ch * 32 + q4 * 8) = out[q4];
         }
-    } else {
-        // warps 10, 11: idle members of the third warpgroup
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     }
 
     tc_fence_before_sync();
