@@ -64,19 +64,22 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons of one GPU.  The sampler is started early (nvidia-smi
+    takes a while to produce its first row); ``mark()`` brackets the timed region and only rows
+    whose host timestamp falls inside it are summarised."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, period_ms: int = 20):
+        self.index, self.rows, self.proc, self.t0, self.t1 = index, [], None, None, None
+        self.period_ms = period_ms
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -86,9 +89,15 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def __exit__(self, *exc):
+    def mark_begin(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
+
+    def stop(self):
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -98,20 +107,21 @@ class ClockSampler:
             self.thread.join(timeout=5)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            if len(r) < 7:
+        for ts, r in self.rows:
+            if len(r) < 7 or self.t0 is None or self.t1 is None or not (self.t0 <= ts <= self.t1 + 0.05):
                 continue
             try:
-                sm.append(float(r[0])); mx.append(float(r[1]))
+                sm.append(float(r[0])); mx.append(float(r[1])); pw.append(float(r[2]))
             except ValueError:
                 continue
             for name, val in zip(names, r[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w": statistics.median(pw) if pw else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
 
 
 def make_inputs(cfg, begin, end, device, chunk=64):
@@ -234,17 +244,20 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---------------------------------------------------------------- device-resident timing
+    clocks = ClockSampler(local_rank).start()
     for _ in range(args.warmup):
         attn([q, kt, v])
     attn.check_status()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
-    with ClockSampler(local_rank) as clocks:
-        ev[0].record()
-        for i in range(args.steps):
-            attn([q, kt, v])
-            ev[i + 1].record()
-        barrier()
+    clocks.mark_begin()
+    ev[0].record()
+    for i in range(args.steps):
+        attn([q, kt, v])
+        ev[i + 1].record()
+    barrier()
+    clocks.mark_end()
+    clocks.stop()
     attn.check_status()
     per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     ms_total = ev[0].elapsed_time(ev[-1])
@@ -325,7 +338,12 @@ def run_ours(args):
             gbs = bytes_alg / (launch_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"]}
-        roof.update({"traffic": None, "kernel": "attention_band_kernel", "peak_source": peaks["source"],
+        # DRAM traffic per launch: ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch over
+        # 16 heads of this workload (profiles/attention_band_kernel_cfg5_16heads.md: 519.1 MB),
+        # scaled by the number of heads (traffic grows in proportion: every head is independent)
+        traffic = 519.1e6 / 16 * heads if (cfg == 5 and args.path == "band") else None
+        roof.update({"traffic": traffic, "traffic_unit": "bytes per launch, scaled from a 16-head ncu capture",
+                     "kernel": "attention_band_kernel", "peak_source": peaks["source"],
                      "peak_kind": "burst", "launch_ms": launch_ms,
                      "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"])
                      if tensor_bound and peaks.get("tflops_sustained") else None,
