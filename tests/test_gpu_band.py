@@ -23,6 +23,14 @@ PATTERNS = [
 ]
 
 
+@pytest.fixture(params=["1", "2"], ids=["one-tile-ctas", "paired-tile-ctas"], autouse=True)
+def band_variant(request, monkeypatch):
+    """Every test runs against both band kernels: one Q tile per CTA (two CTAs per SM) and two Q
+    tiles per CTA.  The library reads the override at each call."""
+    monkeypatch.setenv("SPLAT_B200_BAND_TILES", request.param)
+    return request.param
+
+
 def _run(kind, L, p0, p1, d, dtype, seed, BH=(1, 3), scale=None, spread=1.0):
     import acsr_helpers as ah
     import splat_native as n

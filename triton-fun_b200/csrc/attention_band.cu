@@ -26,6 +26,7 @@
 // class, so they are excluded from the band and written as O[i] = V[start_i]; rows with no
 // non-zero are written as zero.
 #include <limits.h>
+#include <stdlib.h>
 #include <type_traits>
 
 #include "common.cuh"
@@ -536,6 +537,346 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------
+// Single-tile variant: one 128-row Q tile per CTA, 192 threads, 256 tensor-memory columns and
+// ~97 KB of shared memory, so TWO CTAs share an SM and one CTA's prologue / epilogue / waits are
+// covered by the other's work.  K and V travel in 64-key ring items (one math step each).  Each Q
+// tile loads its own K/V, i.e. twice the L2 -> shared-memory traffic of the paired kernel above:
+// used for problems whose classes have a single row tile or too few tile pairs to fill the GPU.
+// Warps: 0-3 softmax/epilogue, 4 = TMA producer, 5 = MMA issuer and tensor-memory owner.
+// ---------------------------------------------------------------------------------------------
+constexpr int kThreads1 = 192;
+constexpr int kTmemCols1 = 256;
+constexpr int kStepBytesPerSub = kStep * 128;   // 64 keys x 128 bytes
+
+struct Control1 {
+    uint64_t q_full;
+    uint64_t kv_full[kStages];
+    uint64_t kv_empty[kStages];
+    uint64_t s_ready[2];
+    uint64_t p_ready[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    int32_t abort_at_entry;
+    int32_t red_lo[4];
+    int32_t red_hi[4];
+};
+
+template <int D> struct Layout1 {
+    static constexpr int kSub = D / 64;
+    static constexpr int kQBytes = kSub * kSubBytes;              // 128 rows
+    static constexpr int kItemBytes = kSub * kStepBytesPerSub;    // 64 keys
+    static constexpr int kRingOff = kQBytes;
+    static constexpr int kCtrlOff = kRingOff + kStages * kItemBytes;
+    static constexpr int kSmemBytes = kCtrlOff + (int)sizeof(Control1) + 1024;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads1, 2)
+attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
+    using L = Layout1<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_q = smem;
+    uint8_t* s_ring = smem + L::kRingOff;
+    Control1* ctrl = reinterpret_cast<Control1*>(smem + L::kCtrlOff);
+    volatile int32_t* status = p.status;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int res = blockIdx.y;
+    const int64_t bh = blockIdx.z;
+    const int u0 = blockIdx.x * kTile;
+
+    if (threadIdx.x == 0) {
+        ctrl->abort_at_entry = *status;
+        mbar_init(&ctrl->q_full, 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&ctrl->kv_full[i], 1);
+            mbar_init(&ctrl->kv_empty[i], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctrl->s_ready[b], 1);
+            mbar_init(&ctrl->p_ready[b], 4);
+        }
+        mbar_init(&ctrl->drain, 1);
+        mbar_fence_init();
+    }
+    int my_a = 0, my_n = 0, row_nnz = 0, row_start = 0;
+    int64_t row_real = -1;
+    if (warp < 4) {
+        const int u = u0 + warp * 32 + lane;
+        int lo = INT_MAX, hi = 0;
+        if (u < p.rows_v) {
+            row_real = (int64_t)u * p.stride + res;
+            const RowAffine ra = row_affine(p.lin, p.tr, p.nnzs, row_real);
+            row_nnz = ra.nnz;
+            row_start = ra.start;
+            if (ra.nnz > 1) {
+                my_a = (ra.start - res) / p.stride;
+                my_n = ra.nnz;
+                lo = my_a / kStep;
+                hi = (my_a + my_n + kStep - 1) / kStep;
+            }
+        }
+        lo = warp_min_i(lo);
+        hi = warp_max_i(hi);
+        if (lane == 0) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
+    }
+    __syncthreads();
+    if (ctrl->abort_at_entry != 0) return;
+    if (warp == 5) {
+        tmem_alloc(&ctrl->tmem_base, kTmemCols1);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    int klo = INT_MAX, khi = 0;
+    for (int w = 0; w < 4; ++w) {
+        klo = min(klo, ctrl->red_lo[w]);
+        khi = max(khi, ctrl->red_hi[w]);
+    }
+    khi = min(khi, (p.rows_v + kStep - 1) / kStep);
+    if (klo >= khi) { klo = 0; khi = 0; }
+    const int steps = khi - klo;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0 && steps > 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            mbar_arrive_expect_tx(&ctrl->q_full, L::kQBytes);
+            for (int sub = 0; sub < L::kSub; ++sub)
+                tma_load_4d(s_q + sub * kSubBytes, &tm_q, &ctrl->q_full, sub * 64, res, u0, (int)bh);
+            int item = 0;
+            bool ok = true;
+            for (int k = klo; k < khi && ok; ++k) {
+                for (int which = 0; which < 2; ++which, ++item) {   // K(k) then V(k)
+                    const int stage = item % kStages;
+                    const uint32_t parity = ((uint32_t)(item / kStages) & 1u) ^ 1u;
+                    if (!mbar_wait(&ctrl->kv_empty[stage], parity, status, kErrKvEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&ctrl->kv_full[stage], L::kItemBytes);
+                    const CUtensorMap* tm = which == 0 ? &tm_k : &tm_v;
+                    for (int sub = 0; sub < L::kSub; ++sub)
+                        tma_load_4d(s_ring + stage * L::kItemBytes + sub * kStepBytesPerSub, tm,
+                                    &ctrl->kv_full[stage], sub * 64, res, k * kStep, (int)bh);
+                }
+            }
+            if (!ok) {
+                mbar_wait_quiet(&ctrl->q_full, 0);
+                for (int i = max(0, item - kStages); i < item; ++i)
+                    mbar_wait_quiet(&ctrl->kv_full[i % kStages], (uint32_t)(i / kStages) & 1u);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        // ring item 2(k - klo) = K(k), 2(k - klo) + 1 = V(k); order S(klo), S(klo+1), then per k:
+        // PV(k), S(k+2)
+        if (lane == 0 && steps > 0) {
+            constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, 0);
+            constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
+            const uint32_t ring_addr = smem_u32(s_ring), q_base = smem_u32(s_q);
+            const uint32_t o_tmem = tmem_base + 2 * kStep;
+            auto full_wait = [&](int item) {
+                return mbar_wait(&ctrl->kv_full[item % kStages], (uint32_t)(item / kStages) & 1u,
+                                 status, kErrKvFull);
+            };
+            auto issue_s = [&](int k) {
+                const uint32_t b_base = ring_addr + ((2 * (k - klo)) % kStages) * L::kItemBytes;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    mma_ss(tmem_base + (k & 1) * kStep,
+                           smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024),
+                           smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024),
+                           idesc_qk, kk > 0);
+            };
+            auto issue_pv = [&](int k, bool acc) {
+                const uint32_t b_base = ring_addr + ((2 * (k - klo) + 1) % kStages) * L::kItemBytes;
+#pragma unroll
+                for (int kk = 0; kk < kStep / 16; ++kk)
+                    mma_ts(o_tmem, tmem_base + (k & 1) * kStep + kk * 8,
+                           smem_desc_sw128(b_base + kk * 2048, kStepBytesPerSub, 1024), idesc_pv,
+                           (acc || kk > 0) ? 1u : 0u);
+            };
+            bool ok = mbar_wait(&ctrl->q_full, 0, status, kErrQ);
+            for (int k = klo; k < min(klo + 2, khi) && ok; ++k) {
+                ok = full_wait(2 * (k - klo));
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_s(k);
+                mma_commit(&ctrl->s_ready[k & 1]);
+                mma_commit(&ctrl->kv_empty[(2 * (k - klo)) % kStages]);
+            }
+            uint32_t p_phase[2] = {0, 0};
+            for (int k = klo; k < khi && ok; ++k) {
+                const int item_v = 2 * (k - klo) + 1;
+                ok = full_wait(item_v);
+                if (!ok) break;
+                ok = mbar_wait(&ctrl->p_ready[k & 1], p_phase[k & 1], status, kErrPReady);
+                if (!ok) break;
+                p_phase[k & 1] ^= 1u;
+                tc_fence_after_sync();
+                issue_pv(k, k > klo);
+                mma_commit(&ctrl->kv_empty[item_v % kStages]);
+                if (k + 2 < khi) {
+                    const int item_k = 2 * (k + 2 - klo);
+                    ok = full_wait(item_k);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_s(k + 2);
+                    mma_commit(&ctrl->kv_empty[item_k % kStages]);
+                }
+                mma_commit(&ctrl->s_ready[k & 1]);   // next scores ready, and PV(k) complete
+            }
+            if (!ok) {
+                mma_commit(&ctrl->drain);
+                mbar_wait_quiet(&ctrl->drain, 0);
+            }
+        }
+    } else if (warp < 4) {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t s_addr = lane_addr;
+        const uint32_t o_addr = lane_addr + 2 * kStep;
+        float m_used = -INFINITY, l_sum = 0.f;
+        uint32_t s_phase[2] = {0, 0};
+        bool pv_waited = false;
+        bool ok = true;
+        const float sc = p.scale_log2;
+        const float2 sc2 = make_float2(sc, sc);
+        for (int k = klo; k < khi; ++k) {
+            const int b = k & 1;
+            if (!pv_waited) {
+                ok = mbar_wait(&ctrl->s_ready[b], s_phase[b], status, kErrSReady);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                s_phase[b] ^= 1u;
+            }
+            pv_waited = false;
+            tc_fence_after_sync();
+            const int c0 = k * kStep;
+            const int v_lo = my_a - c0;
+            const int v_hi = my_n > 0 ? my_a + my_n - c0 : INT_MIN;
+            const bool edge = !__all_sync(0xffffffffu, v_lo <= 0 && v_hi >= kStep);
+            uint32_t r[kStep];
+            tmem_ld32(s_addr + b * kStep, r);
+            tmem_ld32(s_addr + b * kStep + 32, r + 32);
+            tmem_ld_wait();
+            if (edge) {
+#pragma unroll
+                for (int j = 0; j < kStep; ++j)
+                    r[j] = (j >= v_lo && j < v_hi) ? r[j] : 0xff800000u;
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < kStep; j += 8) {
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc)
+                    mx[cc] = fmax3(mx[cc], __uint_as_float(r[j + 2 * cc]), __uint_as_float(r[j + 2 * cc + 1]));
+            }
+            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const float m_new = fmaxf(m_used, mt * sc);
+            const bool need = (m_new - m_used) > kRescaleThreshold;
+            const float corr = need ? ex2(m_used - m_new) : 1.f;
+            if (need) m_used = m_new;
+            l_sum *= corr;
+            const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+            if (k > klo && __any_sync(0xffffffffu, need)) {
+                // PV(k-1) may still be running: its completion is the next arrival on the OTHER
+                // buffer's barrier, consumed here instead of at the top of step k+1
+                ok = mbar_wait(&ctrl->s_ready[b ^ 1], s_phase[b ^ 1], status, kErrSReady);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                s_phase[b ^ 1] ^= 1u;
+                pv_waited = true;
+                tc_fence_after_sync();
+                uint32_t o[32];
+#pragma unroll
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    tmem_ld32(o_addr + ch * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                    tmem_st32(o_addr + ch * 32, o);
+                }
+            }
+            const float2 nm2 = make_float2(-m_eff, -m_eff);
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kStep; j += 4) {
+                float2 a0 = fma2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc2, nm2);
+                float2 a1 = fma2(make_float2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), sc2, nm2);
+                a0.x = ex2(a0.x); a0.y = ex2(a0.y); a1.x = ex2(a1.x); a1.y = ex2(a1.y);
+                acc0 = add2(acc0, a0);
+                acc1 = add2(acc1, a1);
+                r[j >> 1] = pack2<T>(a0.x, a0.y);
+                r[(j >> 1) + 1] = pack2<T>(a1.x, a1.y);
+            }
+            l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+            tmem_st32(s_addr + b * kStep, r);   // P: 32 packed columns over the consumed scores
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctrl->p_ready[b]);
+        }
+        const bool have_o = ok && steps > 0;
+        if (have_o) {
+            for (int i = min(steps, 2); i >= 1 && ok; --i) {
+                const int b = (khi - i) & 1;
+                if (pv_waited && i == 2) continue;
+                ok = mbar_wait(&ctrl->s_ready[b], s_phase[b], status, kErrSReady);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            tc_fence_after_sync();
+        }
+        uint32_t r[32];
+        T* orow = row_real >= 0 ? reinterpret_cast<T*>(p.o) + (bh * p.n_rows + row_real) * D : nullptr;
+        const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
+        const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+            if (have_o && ok) {
+                tmem_ld32(o_addr + ch * 32, r);
+                tmem_ld_wait();
+            }
+            if (orow == nullptr) continue;
+            uint4 out[4];
+            if (row_nnz > 1 && have_o && ok) {
+                uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+#pragma unroll
+                for (int j = 0; j < 32; j += 2)
+                    o32[j >> 1] = pack2<T>(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+            } else if (row_nnz == 1) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    out[q4] = *reinterpret_cast<const uint4*>(vrow + ch * 32 + q4 * 8);
+            } else {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) out[q4] = make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<uint4*>(orow + ch * 32 + q4 * 8) = out[q4];
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -555,16 +896,16 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// (BH, L, d) 16-bit array viewed as (d, stride, L/stride, BH); box (64, 1, 128, 1), 128B swizzle.
+// (BH, L, d) 16-bit array viewed as (d, stride, L/stride, BH); box (64, 1, box_rows, 1), 128B swizzle.
 static bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_rows,
-                     int64_t d, int64_t stride) {
+                     int64_t d, int64_t stride, int box_rows = kTile) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)stride, (cuuint64_t)(n_rows / stride),
                                 (cuuint64_t)bh};
     const cuuint64_t strides[3] = {(cuuint64_t)(d * 2), (cuuint64_t)(stride * d * 2),
                                    (cuuint64_t)(n_rows * d * 2)};
-    const cuuint32_t box[4] = {64, 1, (cuuint32_t)kTile, 1};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult rc = fn(map, dtype == SPLAT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
@@ -590,6 +931,26 @@ static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     dim3 grid((unsigned)pairs, (unsigned)prm.stride, (unsigned)bh);
     kern<<<grid, kThreads, L::kSmemBytes, st>>>(mq, mk, mv, prm);
     return launch_status();
+}
+
+template <typename T, int D>
+static int32_t launch1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                       const Params& prm, int64_t bh, cudaStream_t st) {
+    using L = Layout1<D>;
+    auto kern = attention_band1_kernel<T, D>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) !=
+        cudaSuccess)
+        return SPLAT_ERR_LAUNCH;
+    const int tiles = (prm.rows_v + kTile - 1) / kTile;
+    dim3 grid((unsigned)tiles, (unsigned)prm.stride, (unsigned)bh);
+    kern<<<grid, kThreads1, L::kSmemBytes, st>>>(mq, mk, mv, prm);
+    return launch_status();
+}
+
+template <typename T>
+static int32_t launch1_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                         const Params& prm, int64_t bh, int64_t d, cudaStream_t st) {
+    return d == 128 ? launch1<T, 128>(mq, mk, mv, prm, bh, st) : launch1<T, 64>(mq, mk, mv, prm, bh, st);
 }
 
 template <typename T>
@@ -621,10 +982,18 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     if (plan[5] > n_cols || bh > 65535 || n_rows > INT32_MAX) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SPLAT_ERR_MISALIGNED;
 
+    // One Q tile per CTA (two CTAs per SM) when a class has a single row tile or the paired kernel
+    // would run fewer than ~16 waves (its per-CTA prologue and epilogue are not overlapped);
+    // SPLAT_B200_BAND_TILES=1|2 overrides.
+    const int64_t rows_v = n_rows / stride;
+    const int64_t pair_items = ((rows_v + 2 * band::kTile - 1) / (2 * band::kTile)) * stride * bh;
+    bool single = rows_v <= band::kTile || pair_items < 16 * 148;
+    if (const char* e = getenv("SPLAT_B200_BAND_TILES")) single = e[0] == '1';
+    const int kv_box = single ? band::kStep : band::kTile;
     CUtensorMap mq, mk, mv;
     if (!band::make_map(&mq, q, dtype, bh, n_rows, d, stride) ||
-        !band::make_map(&mk, k, dtype, bh, n_rows, d, stride) ||
-        !band::make_map(&mv, v, dtype, bh, n_rows, d, stride))
+        !band::make_map(&mk, k, dtype, bh, n_rows, d, stride, kv_box) ||
+        !band::make_map(&mv, v, dtype, bh, n_rows, d, stride, kv_box))
         return SPLAT_ERR_DRIVER;
     band::Params prm;
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.o = o; prm.status = status_word;
@@ -633,6 +1002,10 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
 #ifdef SPLAT_BAND_TRACE
     prm.trace = band::g_trace;
 #endif
+    if (single) {
+        if (dtype == SPLAT_BF16) return band::launch1_d<__nv_bfloat16>(mq, mk, mv, prm, bh, d, st);
+        return band::launch1_d<__half>(mq, mk, mv, prm, bh, d, st);
+    }
     if (dtype == SPLAT_BF16) return band::launch_d<__nv_bfloat16>(mq, mk, mv, prm, bh, d, st);
     return band::launch_d<__half>(mq, mk, mv, prm, bh, d, st);
 }
