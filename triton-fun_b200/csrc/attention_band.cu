@@ -573,7 +573,8 @@ template <int D> struct Layout1 {
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads1, 2)
 attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
+                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                       const Params p) {
     using L = Layout1<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -588,8 +589,13 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int64_t bh = blockIdx.z;
     const int u0 = blockIdx.x * kTile;
 
+    // Prologue, one block-wide barrier: tensor-memory allocation (warp 5), barrier initialisation
+    // (thread 0) and the row metadata (softmax warps) proceed side by side.
+    if (warp == 5) {
+        tmem_alloc(&ctrl->tmem_base, kTmemCols1);
+        tmem_relinquish();
+    }
     if (threadIdx.x == 0) {
-        ctrl->abort_at_entry = *status;
         mbar_init(&ctrl->q_full, 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&ctrl->kv_full[i], 1);
@@ -601,6 +607,7 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         mbar_init(&ctrl->drain, 1);
         mbar_fence_init();
+        ctrl->abort_at_entry = *status;
     }
     int my_a = 0, my_n = 0, row_nnz = 0, row_start = 0;
     int64_t row_real = -1;
@@ -623,16 +630,14 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         hi = warp_max_i(hi);
         if (lane == 0) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
     }
-    __syncthreads();
-    if (ctrl->abort_at_entry != 0) return;
-    if (warp == 5) {
-        tmem_alloc(&ctrl->tmem_base, kTmemCols1);
-        tmem_relinquish();
-    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
+    if (ctrl->abort_at_entry != 0) {   // an earlier CTA gave up: release tensor memory and leave
+        if (warp == 5) tmem_dealloc(tmem_base, kTmemCols1);
+        return;
+    }
 
     int klo = INT_MAX, khi = 0;
     for (int w = 0; w < 4; ++w) {
@@ -837,8 +842,12 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             tc_fence_after_sync();
         }
+        // epilogue: O / l for band rows, V[start] for single-element rows, zero otherwise.  Rows are
+        // staged in the Q buffer (free: every MMA has completed) in the 128-byte-swizzled tile
+        // layout and leave through one tiled TMA store per 64-column half (rows past the end of
+        // the class are clipped by the tensor map).
         uint32_t r[32];
-        T* orow = row_real >= 0 ? reinterpret_cast<T*>(p.o) + (bh * p.n_rows + row_real) * D : nullptr;
+        const int t = warp * 32 + lane;
         const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
 #pragma unroll
@@ -847,14 +856,13 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tmem_ld32(o_addr + ch * 32, r);
                 tmem_ld_wait();
             }
-            if (orow == nullptr) continue;
             uint4 out[4];
             if (row_nnz > 1 && have_o && ok) {
                 uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
 #pragma unroll
                 for (int j = 0; j < 32; j += 2)
                     o32[j >> 1] = pack2<T>(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
-            } else if (row_nnz == 1) {
+            } else if (row_nnz == 1 && row_real >= 0) {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
                     out[q4] = *reinterpret_cast<const uint4*>(vrow + ch * 32 + q4 * 8);
@@ -862,9 +870,19 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) out[q4] = make_uint4(0, 0, 0, 0);
             }
+            // columns [32 ch, 32 ch + 32) = 16-byte chunks 4 (ch & 1) .. +3 of 64-column half ch >> 1
+            uint8_t* srow = s_q + (ch >> 1) * kSubBytes + t * 128;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4)
-                *reinterpret_cast<uint4*>(orow + ch * 32 + q4 * 8) = out[q4];
+                *reinterpret_cast<uint4*>(srow + ((((ch & 1) * 4 + q4) ^ (t & 7)) << 4)) = out[q4];
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four softmax warps, unconditionally
+        if (threadIdx.x == 0) {
+            for (int sub = 0; sub < L::kSub; ++sub)
+                tma_store_4d(&tm_o, s_q + sub * kSubBytes, sub * 64, res, u0, (int)bh);
+            tma_store_commit();
+            tma_store_wait_read();
         }
     }
     tc_fence_before_sync();
@@ -935,7 +953,7 @@ static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 
 template <typename T, int D>
 static int32_t launch1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                       const Params& prm, int64_t bh, cudaStream_t st) {
+                       const CUtensorMap& mo, const Params& prm, int64_t bh, cudaStream_t st) {
     using L = Layout1<D>;
     auto kern = attention_band1_kernel<T, D>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) !=
@@ -943,14 +961,15 @@ static int32_t launch1(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
         return SPLAT_ERR_LAUNCH;
     const int tiles = (prm.rows_v + kTile - 1) / kTile;
     dim3 grid((unsigned)tiles, (unsigned)prm.stride, (unsigned)bh);
-    kern<<<grid, kThreads1, L::kSmemBytes, st>>>(mq, mk, mv, prm);
+    kern<<<grid, kThreads1, L::kSmemBytes, st>>>(mq, mk, mv, mo, prm);
     return launch_status();
 }
 
 template <typename T>
 static int32_t launch1_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                         const Params& prm, int64_t bh, int64_t d, cudaStream_t st) {
-    return d == 128 ? launch1<T, 128>(mq, mk, mv, prm, bh, st) : launch1<T, 64>(mq, mk, mv, prm, bh, st);
+                         const CUtensorMap& mo, const Params& prm, int64_t bh, int64_t d, cudaStream_t st) {
+    return d == 128 ? launch1<T, 128>(mq, mk, mv, mo, prm, bh, st)
+                    : launch1<T, 64>(mq, mk, mv, mo, prm, bh, st);
 }
 
 template <typename T>
@@ -990,10 +1009,11 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     bool single = rows_v <= band::kTile || pair_items < 16 * 148;
     if (const char* e = getenv("SPLAT_B200_BAND_TILES")) single = e[0] == '1';
     const int kv_box = single ? band::kStep : band::kTile;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;
     if (!band::make_map(&mq, q, dtype, bh, n_rows, d, stride) ||
         !band::make_map(&mk, k, dtype, bh, n_rows, d, stride, kv_box) ||
-        !band::make_map(&mv, v, dtype, bh, n_rows, d, stride, kv_box))
+        !band::make_map(&mv, v, dtype, bh, n_rows, d, stride, kv_box) ||
+        !band::make_map(&mo, o, dtype, bh, n_rows, d, stride))
         return SPLAT_ERR_DRIVER;
     band::Params prm;
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.o = o; prm.status = status_word;
@@ -1003,8 +1023,8 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     prm.trace = band::g_trace;
 #endif
     if (single) {
-        if (dtype == SPLAT_BF16) return band::launch1_d<__nv_bfloat16>(mq, mk, mv, prm, bh, d, st);
-        return band::launch1_d<__half>(mq, mk, mv, prm, bh, d, st);
+        if (dtype == SPLAT_BF16) return band::launch1_d<__nv_bfloat16>(mq, mk, mv, mo, prm, bh, d, st);
+        return band::launch1_d<__half>(mq, mk, mv, mo, prm, bh, d, st);
     }
     if (dtype == SPLAT_BF16) return band::launch_d<__nv_bfloat16>(mq, mk, mv, prm, bh, d, st);
     return band::launch_d<__half>(mq, mk, mv, prm, bh, d, st);
