@@ -143,7 +143,8 @@ __device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                      const __grid_constant__ CUtensorMap tm_v, const Params p) {
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                      const Params p) {
     using L = Layout<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -163,8 +164,13 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int64_t bh = blockIdx.z;
     const int u0 = pair * 2 * kTile;
 
+    // Prologue, one block-wide barrier: tensor-memory allocation (MMA warp), barrier initialisation
+    // (thread 0) and the row metadata (softmax warps) proceed side by side.
+    if (warp == kMmaWarp) {
+        tmem_alloc(&ctrl->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
     if (threadIdx.x == 0) {
-        ctrl->abort_at_entry = *status;
         mbar_init(&ctrl->q_full, 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&ctrl->kv_full[i], 1);
@@ -178,6 +184,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(&ctrl->drain[i], 1);
         }
         mbar_fence_init();
+        ctrl->abort_at_entry = *status;
     }
 
     // Per-row metadata in class coordinates (softmax threads only).
@@ -203,17 +210,14 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         hi = warp_max_i(hi);
         if (lane == 0) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
     }
-    __syncthreads();
-    if (ctrl->abort_at_entry != 0) return;  // an earlier CTA gave up: do nothing
-
-    if (warp == kMmaWarp) {
-        tmem_alloc(&ctrl->tmem_base, kTmemCols);
-        tmem_relinquish();
-    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
+    if (ctrl->abort_at_entry != 0) {   // an earlier CTA gave up: release tensor memory and leave
+        if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
+        return;
+    }
 
     // Step ranges [klo, khi) (64-key units) of the two Q tiles and the ring-tile range of their union.
     int klo[2], khi[2];
@@ -495,9 +499,13 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
             tc_fence_after_sync();
         }
-        // epilogue: O / l for band rows, V[start] for single-element rows, zero otherwise
+        // epilogue: O / l for band rows, V[start] for single-element rows, zero otherwise.  Rows are
+        // staged in the tile's Q buffer (free: every MMA of the tile has completed) in the
+        // 128-byte-swizzled layout and leave through one tiled TMA store per 64-column half (rows
+        // past the end of the class are clipped by the tensor map).
         uint32_t r[32];
-        T* orow = row_real >= 0 ? reinterpret_cast<T*>(p.o) + (bh * p.n_rows + row_real) * D : nullptr;
+        const int t = (warp & 3) * 32 + lane;
+        uint8_t* s_o = s_q + x * L::kTileBytes;
         const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
 #pragma unroll
@@ -506,14 +514,13 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tmem_ld32(o_addr + ch * 32, r);
                 tmem_ld_wait();
             }
-            if (orow == nullptr) continue;
             uint4 out[4];
             if (row_nnz > 1 && have_o && ok) {
                 uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
 #pragma unroll
                 for (int j = 0; j < 32; j += 2)
                     o32[j >> 1] = pack2<T>(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
-            } else if (row_nnz == 1) {
+            } else if (row_nnz == 1 && row_real >= 0) {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
                     out[q4] = *reinterpret_cast<const uint4*>(vrow + ch * 32 + q4 * 8);
@@ -521,9 +528,18 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) out[q4] = make_uint4(0, 0, 0, 0);
             }
+            uint8_t* srow = s_o + (ch >> 1) * kSubBytes + t * 128;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4)
-                *reinterpret_cast<uint4*>(orow + ch * 32 + q4 * 8) = out[q4];
+                *reinterpret_cast<uint4*>(srow + ((((ch & 1) * 4 + q4) ^ (t & 7)) << 4)) = out[q4];
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");   // the tile's four softmax warps
+        if ((warp & 3) == 0 && lane == 0 && u0 + x * kTile < p.rows_v) {
+            for (int sub = 0; sub < L::kSub; ++sub)
+                tma_store_4d(&tm_o, s_o + sub * kSubBytes, sub * 64, res, u0 + x * kTile, (int)bh);
+            tma_store_commit();
+            tma_store_wait_read();
         }
     }
 
@@ -939,7 +955,7 @@ static long long* g_trace = nullptr;
 
 template <typename T, int D>
 static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                      const Params& prm, int64_t bh, cudaStream_t st) {
+                      const CUtensorMap& mo, const Params& prm, int64_t bh, cudaStream_t st) {
     using L = Layout<D>;
     auto kern = attention_band_kernel<T, D>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) !=
@@ -947,7 +963,7 @@ static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
         return SPLAT_ERR_LAUNCH;
     const int pairs = (prm.rows_v + 2 * kTile - 1) / (2 * kTile);
     dim3 grid((unsigned)pairs, (unsigned)prm.stride, (unsigned)bh);
-    kern<<<grid, kThreads, L::kSmemBytes, st>>>(mq, mk, mv, prm);
+    kern<<<grid, kThreads, L::kSmemBytes, st>>>(mq, mk, mv, mo, prm);
     return launch_status();
 }
 
@@ -974,8 +990,9 @@ static int32_t launch1_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
 
 template <typename T>
 static int32_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                        const Params& prm, int64_t bh, int64_t d, cudaStream_t st) {
-    return d == 128 ? launch<T, 128>(mq, mk, mv, prm, bh, st) : launch<T, 64>(mq, mk, mv, prm, bh, st);
+                        const CUtensorMap& mo, const Params& prm, int64_t bh, int64_t d, cudaStream_t st) {
+    return d == 128 ? launch<T, 128>(mq, mk, mv, mo, prm, bh, st)
+                    : launch<T, 64>(mq, mk, mv, mo, prm, bh, st);
 }
 
 }  // namespace band
@@ -1026,8 +1043,8 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
         if (dtype == SPLAT_BF16) return band::launch1_d<__nv_bfloat16>(mq, mk, mv, mo, prm, bh, d, st);
         return band::launch1_d<__half>(mq, mk, mv, mo, prm, bh, d, st);
     }
-    if (dtype == SPLAT_BF16) return band::launch_d<__nv_bfloat16>(mq, mk, mv, prm, bh, d, st);
-    return band::launch_d<__half>(mq, mk, mv, prm, bh, d, st);
+    if (dtype == SPLAT_BF16) return band::launch_d<__nv_bfloat16>(mq, mk, mv, mo, prm, bh, d, st);
+    return band::launch_d<__half>(mq, mk, mv, mo, prm, bh, d, st);
 }
 
 }  // namespace splat
