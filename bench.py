@@ -338,11 +338,13 @@ def run_ours(args):
             gbs = bytes_alg / (launch_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"]}
-        # DRAM traffic per launch: ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch over
-        # 16 heads of this workload (profiles/attention_band_kernel_cfg5_16heads.md: 519.1 MB),
-        # scaled by the number of heads (traffic grows in proportion: every head is independent)
-        traffic = 519.1e6 / 16 * heads if (cfg == 5 and args.path == "band") else None
-        roof.update({"traffic": traffic, "traffic_unit": "bytes per launch, scaled from a 16-head ncu capture",
+        # DRAM traffic per launch from the ncu captures summarised under profiles/
+        # (dram__bytes_read.sum + dram__bytes_write.sum).  Configuration 5 was captured on 16 of its
+        # 512 heads (520.0 MB) and is scaled by the head count: traffic grows in proportion, every
+        # head being independent.  Configurations 2-4 were captured at full size.
+        ncu_traffic_per_head = {5: 520.0e6 / 16, 2: 117.5e6 / 64, 3: 515.1e6 / 64, 4: 519.1e6 / 32}
+        traffic = ncu_traffic_per_head[cfg] * heads if args.path == "band" else None
+        roof.update({"traffic": traffic, "traffic_unit": "bytes per launch (ncu capture scaled by heads, see profiles/)",
                      "kernel": "attention_band_kernel", "peak_source": peaks["source"],
                      "peak_kind": "burst", "launch_ms": launch_ms,
                      "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"])

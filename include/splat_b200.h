@@ -174,6 +174,12 @@ int32_t splat_attention_noalloc(const void* q, const void* k, int64_t k_stride_b
                                 int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                                 int64_t trailing_dim, float scale, int32_t dtype, void* stream);
 
+/* Self-test of the bounded device-side wait used by the tensor-core kernels: one CTA waits on an
+ * mbarrier that nothing arrives on, gives up after limit_cycles SM clocks (1 .. 2e9), stores code
+ * 99 in *status_word (device int32, cleared by the caller) and ends normally; the context stays
+ * usable.  No counterpart in the reference. */
+int32_t splat_selftest_bounded_wait(int32_t* status_word, int64_t limit_cycles, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -103,3 +103,34 @@ def test_band_path_refuses_what_it_cannot_do():
         n.attention_fused(q32, q32.transpose(2, 3), q32, torch.empty_like(q32), acsr[2], acsr[3],
                           acsr[4], 1.0, n.PATH_BAND)
     torch.cuda.synchronize()
+
+
+def test_bounded_wait_gives_up_and_reports(band_variant):
+    """A device-side wait that can never complete (an mbarrier nothing arrives on) must run out
+    after its cycle limit, leave code 99 in the status word and end the kernel normally; the band
+    kernel must still work afterwards and must do nothing while the status word is set."""
+    import acsr_helpers as ah
+    import splat_native as n
+    if band_variant != "1":
+        pytest.skip("one run is enough")
+    word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = n._lib.splat_selftest_bounded_wait(word.data_ptr(), 200000, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert word.item() == 99
+    # a band kernel launched while the status word is set leaves the output untouched ...
+    L, d = 256, 64
+    acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 63), 16, 0)
+    q = torch.randn(1, 1, L, d, device="cuda").to(torch.bfloat16)
+    sw = n.status_word(torch.device("cuda", 0))
+    sw.fill_(7)
+    out = torch.full_like(q, 3.0)
+    n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+    torch.cuda.synchronize()
+    assert (out == 3.0).all()
+    with pytest.raises(RuntimeError):
+        n.check_status_word(0)          # reports and clears
+    # ... and works again once it is cleared
+    n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+    n.check_status_word(0)
+    assert torch.isfinite(out.float()).all() and not (out == 3.0).all()

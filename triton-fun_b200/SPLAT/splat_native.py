@@ -37,6 +37,7 @@ SIGNATURES = {
     "splat_spmm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
     "splat_attention_fused": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                               _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
+    "splat_selftest_bounded_wait": [_vp, _i64, _vp],
     "splat_attention_noalloc": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                 _i64, _i64, _i64, _f32, _i32, _vp],
 }

@@ -1,6 +1,7 @@
 // Entry points that are not tied to one kernel file: version, status strings and the dispatch of
 // the fused attention call between the tensor-core band kernel and the general CUDA-core kernel.
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace splat {
 int32_t attention_generic(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
@@ -14,6 +15,27 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
                        float scale, int32_t dtype, const int32_t* plan, int32_t* status_word,
                        cudaStream_t st);
 }  // namespace splat
+
+namespace splat {
+// One CTA waits, with the same bounded wait the band kernels use, on an mbarrier that nothing ever
+// arrives on.  The wait must give up after limit_cycles, record the code and let the kernel end.
+__global__ void bounded_wait_selftest_kernel(int32_t* status_word, long long limit_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        tc::mbar_fence_init();
+    }
+    __syncthreads();
+    const bool ok = tc::mbar_wait(&bar, 0, status_word, 99, limit_cycles);
+    if (ok) atomicExch(status_word, -1);   // cannot happen: nobody arrives
+}
+}  // namespace splat
+
+extern "C" int32_t splat_selftest_bounded_wait(int32_t* status_word, int64_t limit_cycles, void* stream) {
+    if (!status_word || limit_cycles < 1 || limit_cycles > 2000000000LL) return SPLAT_ERR_BAD_ARG;
+    splat::bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status_word, limit_cycles);
+    return splat::launch_status();
+}
 
 extern "C" int32_t splat_version(void) { return SPLAT_B200_VERSION; }
 
