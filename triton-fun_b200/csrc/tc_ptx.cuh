@@ -70,7 +70,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     const long long t0 = clock64();
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++polls & 0x3fu) == 0) {
+        if ((++polls & 0x3ffu) == 0) {
             if (*status_word != 0) return false;
             if (clock64() - t0 > limit_cycles) {
                 atomicCAS((int32_t*)status_word, 0, code);
