@@ -20,6 +20,8 @@
  * sTod_tr and nnzs are read, as in the reference kernels) and recover integers as
  *     stride = rint(sTod_lin), start = rint(sTod_tr * sTod_lin), nnz = rint(nnzs).
  * Sparse operands are stored as (BH, L, trailing_dim) with trailing_dim = max_i nnz_i.
+ * A problem with no work (BH * L = 0) returns SPLAT_OK without a launch; its data pointers may be
+ * null (an empty torch tensor has a null data pointer).
  */
 #ifndef SPLAT_B200_H
 #define SPLAT_B200_H

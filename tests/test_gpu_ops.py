@@ -181,3 +181,41 @@ def test_module_unfused_and_fused_agree_with_oracle(golden_meta):
     qp, kp, vp = (torch.einsum('bsd,dnh->bnsh', x, t) for t in w)
     assert_close(out, at.attention_acsr(qp, kp.transpose(2, 3), vp, ref, 32, d ** -0.5),
                  torch.float32, "unit")
+
+
+def test_empty_batch_and_rows_without_nonzeros():
+    """Edge inputs: a batch of zero heads launches nothing and returns; rows of the mask with no
+    non-zero give zero output rows and rows with one non-zero copy the V row the metadata names
+    (column 0: the reference describes single-element rows that way), on every path."""
+    import acsr_helpers as ah
+    import splat_native as n
+    torch.manual_seed(11)
+    L, d = 256, 64
+    mask = ao.causal_windowed_mask(L, 40)
+    mask[5:9, :] = 0            # empty rows
+    mask[100, :] = 0
+    mask[100, 37] = 1           # one non-zero, not at column 0
+    mask[255, :] = 0            # last row empty
+    meta = ao.metadata_from_mask(mask, 16)
+    acsr = ah.create_acsr(mask.tolist(), 16, 0)
+    for dtype in (torch.float32, torch.bfloat16):
+        q, k, v = (torch.randn(1, 2, L, d).to(dtype) for _ in range(3))
+        ref = at.attention_acsr(q, k.transpose(2, 3), v, meta, meta["trailing_dim"], d ** -0.5)
+        assert torch.count_nonzero(ref[:, :, 5:9]) == 0 and torch.count_nonzero(ref[:, :, 255]) == 0
+        assert torch.equal(ref[:, :, 100], v[:, :, 0].float())
+        for path in (n.PATH_GENERIC, n.PATH_AUTO):
+            out = torch.full((1, 2, L, d), float("nan"), dtype=dtype, device="cuda")
+            n.attention_fused(q.cuda(), k.cuda().transpose(2, 3), v.cuda(), out, acsr[2], acsr[3],
+                              acsr[4], d ** -0.5, path)
+            n.check_status_word(0)
+            assert_close(out, ref, dtype, f"empty rows path={path} {dtype}")
+    # zero heads: every entry point returns without a launch
+    q0 = torch.empty(0, 2, L, d, device="cuda")
+    out0 = torch.empty(0, 2, L, d, device="cuda")
+    n.attention_fused(q0, q0.transpose(2, 3), q0, out0, acsr[2], acsr[3], acsr[4], 1.0, n.PATH_AUTO)
+    s0 = torch.empty(0, 2, L, meta["trailing_dim"], device="cuda")
+    T = meta["trailing_dim"]
+    n.sddmm(q0, q0.transpose(2, 3), s0, acsr[2], acsr[3], acsr[4], T)
+    n.softmax(s0, s0, acsr[4], T)
+    n.spmm(s0, q0, out0, acsr[2], acsr[3], acsr[4], T)
+    torch.cuda.synchronize()

@@ -1002,8 +1002,9 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
                        const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                        float scale, int32_t dtype, const int32_t* plan, int32_t* status_word,
                        cudaStream_t st) {
-    if (!q || !k || !v || !o || !lin || !tr || !nnzs || !plan || !status_word || bh < 0 ||
-        n_rows < 0)
+    if (bh < 0 || n_rows < 0) return SPLAT_ERR_BAD_ARG;
+    if (bh == 0 || n_rows == 0) return SPLAT_ERR_UNSUPPORTED_SHAPE;   // empty: left to the generic path
+    if (!q || !k || !v || !o || !lin || !tr || !nnzs || !plan || !status_word)
         return SPLAT_ERR_BAD_ARG;
     if (dtype != SPLAT_F16 && dtype != SPLAT_BF16) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (d != 64 && d != 128) return SPLAT_ERR_UNSUPPORTED_SHAPE;

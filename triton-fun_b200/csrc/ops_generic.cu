@@ -396,9 +396,9 @@ int32_t attention_generic(const void* q, const void* k, int64_t ksb, int64_t ksc
                           const void* v, void* o, const float* lin, const float* tr,
                           const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                           float scale, int32_t dtype, cudaStream_t st) {
-    if (!q || !k || !v || !o || !lin || !tr || !nnzs || !sizes_ok(bh, n_rows, n_cols, d, 0))
-        return SPLAT_ERR_BAD_ARG;
-    if (bh * n_rows == 0) return SPLAT_OK;
+    if (!sizes_ok(bh, n_rows, n_cols, d, 0)) return SPLAT_ERR_BAD_ARG;
+    if (bh * n_rows == 0) return SPLAT_OK;   // empty batch: nothing to read or write, pointers may be null
+    if (!q || !k || !v || !o || !lin || !tr || !nnzs) return SPLAT_ERR_BAD_ARG;
     switch (dtype) {
         case SPLAT_F32: return attention_t<float>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, st);
         case SPLAT_F16: return attention_t<__half>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, st);
@@ -416,10 +416,9 @@ extern "C" int32_t splat_sddmm(const void* q, const void* k, int64_t k_stride_bh
                                const float* sTod_lin, const float* sTod_tr, const float* nnzs,
                                int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                                int64_t trailing_dim, int32_t dtype, void* stream) {
-    if (!q || !k || !s_out || !sTod_lin || !sTod_tr || !nnzs ||
-        !sizes_ok(bh, n_rows, n_cols, d, trailing_dim))
-        return SPLAT_ERR_BAD_ARG;
-    if (bh * n_rows * trailing_dim == 0) return SPLAT_OK;
+    if (!sizes_ok(bh, n_rows, n_cols, d, trailing_dim)) return SPLAT_ERR_BAD_ARG;
+    if (bh * n_rows * trailing_dim == 0) return SPLAT_OK;   // empty: pointers may be null
+    if (!q || !k || !s_out || !sTod_lin || !sTod_tr || !nnzs) return SPLAT_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
         case SPLAT_F32: return sddmm_t<float>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, d, trailing_dim, st);
@@ -432,9 +431,9 @@ extern "C" int32_t splat_sddmm(const void* q, const void* k, int64_t k_stride_bh
 extern "C" int32_t splat_softmax(const void* s_in, void* p_out, const float* nnzs, int64_t bh,
                                  int64_t n_rows, int64_t trailing_dim, float scale, int32_t dtype,
                                  void* stream) {
-    if (!s_in || !p_out || !nnzs || !sizes_ok(bh, n_rows, 0, 1, trailing_dim))
-        return SPLAT_ERR_BAD_ARG;
-    if (bh * n_rows * trailing_dim == 0) return SPLAT_OK;
+    if (!sizes_ok(bh, n_rows, 0, 1, trailing_dim)) return SPLAT_ERR_BAD_ARG;
+    if (bh * n_rows * trailing_dim == 0) return SPLAT_OK;   // empty: pointers may be null
+    if (!s_in || !p_out || !nnzs) return SPLAT_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
         case SPLAT_F32: return softmax_t<float>(s_in, p_out, nnzs, bh, n_rows, trailing_dim, scale, st);
@@ -448,10 +447,9 @@ extern "C" int32_t splat_spmm(const void* p, const void* v, void* o, const float
                               const float* sTod_tr, const float* nnzs, int64_t bh, int64_t n_rows,
                               int64_t n_cols, int64_t d, int64_t trailing_dim, int32_t dtype,
                               void* stream) {
-    if (!p || !v || !o || !sTod_lin || !sTod_tr || !nnzs ||
-        !sizes_ok(bh, n_rows, n_cols, d, trailing_dim))
-        return SPLAT_ERR_BAD_ARG;
-    if (bh * n_rows == 0) return SPLAT_OK;
+    if (!sizes_ok(bh, n_rows, n_cols, d, trailing_dim)) return SPLAT_ERR_BAD_ARG;
+    if (bh * n_rows == 0) return SPLAT_OK;   // empty: pointers may be null
+    if (!p || !v || !o || !sTod_lin || !sTod_tr || !nnzs) return SPLAT_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
         case SPLAT_F32: return spmm_t<float>(p, v, o, sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, trailing_dim, st);
