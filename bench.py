@@ -227,7 +227,11 @@ def run_ours(args):
 
     mask = ah.PatternMask(KIND[pat], L, p0, p1)
     t0 = time.perf_counter()
+    unfused = args.path == "unfused"
+    if unfused:
+        args.no_e2e = True   # forward_host streams the fused kernel only
     attn = r_attention.RegularAttention(1, L, heads, d, mask, 16, 16, dev, dtype, scale=scale,
+                                        fused=not unfused,
                                         path=n.PATH_BAND if args.path == "band" else
                                         (n.PATH_GENERIC if args.path == "generic" else n.PATH_AUTO))
     torch.cuda.synchronize()
@@ -328,9 +332,11 @@ def run_ours(args):
         launch_ms = statistics.mean(per_launch)
         achieved = flops_per_head * heads / (launch_ms * 1e-3) / 1e12
         bytes_alg = 4.0 * L * d * q.element_size() * heads
+        if unfused:   # S written and read, P written and read, on top of Q, K, V, O
+            bytes_alg += 4.0 * L * int(attn.acsr_trailing_dim) * q.element_size() * heads
         t_flop = flops_per_head * heads / (peaks["tflops"] * 1e12)
         t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
-        tensor_bound = t_flop >= t_hbm
+        tensor_bound = t_flop >= t_hbm and not unfused
         if tensor_bound:
             roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["tflops"]}
@@ -345,7 +351,9 @@ def run_ours(args):
         ncu_traffic_per_head = {5: 520.0e6 / 16, 2: 117.5e6 / 64, 3: 515.1e6 / 64, 4: 519.1e6 / 32}
         traffic = ncu_traffic_per_head[cfg] * heads if args.path == "band" else None
         roof.update({"traffic": traffic, "traffic_unit": "bytes per launch (ncu capture scaled by heads, see profiles/)",
-                     "kernel": "attention_band_kernel", "peak_source": peaks["source"],
+                     "kernel": "sddmm + softmax + spmm (three launches)" if unfused else
+                               ("attention_band_kernel" if args.path == "band" else "attention_rows_kernel"),
+                     "peak_source": peaks["source"],
                      "peak_kind": "burst", "launch_ms": launch_ms,
                      "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"])
                      if tensor_bound and peaks.get("tflops_sustained") else None,
@@ -361,7 +369,7 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (per-GPU Q+K+V = %.0f MB)" % (3 * heads * L * d * q.element_size() / 1e6),
                        "path": args.path},
             "e2e": e2e, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks.summary(),
-            "gpu_launches": args.steps * world, "metadata_build_ms": metadata_ms,
+            "gpu_launches": args.steps * world * (3 if unfused else 1), "metadata_build_ms": metadata_ms,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -376,7 +384,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
-    ap.add_argument("--path", default="band", choices=["band", "generic", "auto"])
+    ap.add_argument("--path", default="band", choices=["band", "generic", "auto", "unfused"],
+                    help="fused kernel choice, or 'unfused': the reference's three launches (SDDMM, softmax, SpMM)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

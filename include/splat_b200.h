@@ -176,6 +176,22 @@ int32_t splat_attention_noalloc(const void* q, const void* k, int64_t k_stride_b
                                 int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                                 int64_t trailing_dim, float scale, int32_t dtype, void* stream);
 
+/* Tensor-core SDDMM and SpMM for ACSR patterns whose rows are contiguous bands after regrouping by
+ * residue class (the condition of SPLAT_PATH_BAND above): same operands and results as splat_sddmm /
+ * splat_spmm (replacing SPLAT/r_sddmm.py:171-184 and SPLAT/r_spmm.py:148-164 for such patterns),
+ * 16-bit dtypes, d = 64 or 128, K given as the transposed view of a contiguous (BH, L, d) array.
+ * plan_i32 = the 8 host integers of splat_acsr_classify, status_word as in splat_attention_fused.
+ * SPLAT_ERR_UNSUPPORTED_SHAPE means "use splat_sddmm / splat_spmm"; nothing was launched. */
+int32_t splat_sddmm_band(const void* q, const void* k, int64_t k_stride_bh, int64_t k_stride_col,
+                         int64_t k_stride_k, void* s_out, const float* sTod_lin, const float* sTod_tr,
+                         const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
+                         int64_t trailing_dim, int32_t dtype, const int32_t* plan_i32,
+                         int32_t* status_word, void* stream);
+int32_t splat_spmm_band(const void* p, const void* v, void* o, const float* sTod_lin,
+                        const float* sTod_tr, const float* nnzs, int64_t bh, int64_t n_rows,
+                        int64_t n_cols, int64_t d, int64_t trailing_dim, int32_t dtype,
+                        const int32_t* plan_i32, int32_t* status_word, void* stream);
+
 /* Self-test of the bounded device-side wait used by the tensor-core kernels: one CTA waits on an
  * mbarrier that nothing arrives on, gives up after limit_cycles SM clocks (1 .. 2e9), stores code
  * 99 in *status_word (device int32, cleared by the caller) and ends normally; the context stays

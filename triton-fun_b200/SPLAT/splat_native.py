@@ -37,6 +37,10 @@ SIGNATURES = {
     "splat_spmm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
     "splat_attention_fused": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                               _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
+    "splat_sddmm_band": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
+                         _i32, _vp, _vp, _vp],
+    "splat_spmm_band": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp,
+                        _vp],
     "splat_selftest_bounded_wait": [_vp, _i64, _vp],
     "splat_attention_noalloc": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                 _i64, _i64, _i64, _f32, _i32, _vp],
@@ -211,7 +215,15 @@ def _contig(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
-def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int) -> None:
+ERR_UNSUPPORTED_SHAPE = -6
+
+
+def _band_candidate(x: torch.Tensor, path: int) -> bool:
+    """The tensor-core kernels take 16-bit operands with d = 64 or 128 (the library checks the rest)."""
+    return path != PATH_GENERIC and x.dtype in (torch.float16, torch.bfloat16) and x.numel() > 0
+
+
+def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = PATH_AUTO) -> None:
     dev = x.device
     _contig(x, "x"); _contig(output, "output")
     B, H, L, d = x.shape
@@ -221,6 +233,21 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int) -> None:
         raise ValueError("sddmm: inconsistent operand shapes or dtypes")
     if tuple(output.shape) != (B, H, L, trailing_dim):
         raise ValueError(f"sddmm: output must have shape {(B, H, L, trailing_dim)}")
+    if _band_candidate(x, path) and ksk == 1 and ksc == d and ksb == n_cols * d:
+        plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
+        with torch.cuda.device(dev):
+            rc = _lib.splat_sddmm_band(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
+                                       _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
+                                       _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, trailing_dim,
+                                       dtype_code(x.dtype), ctypes.cast(plan_arr, ctypes.c_void_p),
+                                       status_word(dev).data_ptr(), _stream(dev))
+        if rc != ERR_UNSUPPORTED_SHAPE:
+            check(rc, "splat_sddmm_band")
+            if os.environ.get("SPLAT_B200_DEBUG"):
+                check_status_word(dev)
+            return
+    if path == PATH_BAND:
+        raise RuntimeError("sddmm: the band path does not apply to these operands")
     with torch.cuda.device(dev):
         check(_lib.splat_sddmm(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
                                _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
@@ -240,7 +267,7 @@ def softmax(x, output, nnzs, trailing_dim: int, scale: float = 1.0) -> None:
               "splat_softmax")
 
 
-def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int) -> None:
+def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = PATH_AUTO) -> None:
     dev = x.device
     _contig(x, "x"); _contig(y, "y"); _contig(output, "output")
     B, H, L, T = x.shape
@@ -248,6 +275,21 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int) -> None:
     if T != trailing_dim or tuple(output.shape) != (B, H, L, d) or y.dtype != x.dtype or \
             output.dtype != x.dtype or y.shape[:2] != x.shape[:2]:
         raise ValueError("spmm: inconsistent operand shapes or dtypes")
+    if _band_candidate(x, path):
+        plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
+        with torch.cuda.device(dev):
+            rc = _lib.splat_spmm_band(x.data_ptr(), y.data_ptr(), output.data_ptr(),
+                                      _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
+                                      _f32_vec(nnzs, L, "nnzs"), B * H, L, n_cols, d, T,
+                                      dtype_code(x.dtype), ctypes.cast(plan_arr, ctypes.c_void_p),
+                                      status_word(dev).data_ptr(), _stream(dev))
+        if rc != ERR_UNSUPPORTED_SHAPE:
+            check(rc, "splat_spmm_band")
+            if os.environ.get("SPLAT_B200_DEBUG"):
+                check_status_word(dev)
+            return
+    if path == PATH_BAND:
+        raise RuntimeError("spmm: the band path does not apply to these operands")
     with torch.cuda.device(dev):
         check(_lib.splat_spmm(x.data_ptr(), y.data_ptr(), output.data_ptr(),
                               _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),

@@ -931,8 +931,9 @@ static EncodeTiledFn encode_fn() {
 }
 
 // (BH, L, d) 16-bit array viewed as (d, stride, L/stride, BH); box (64, 1, box_rows, 1), 128B swizzle.
-static bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_rows,
-                     int64_t d, int64_t stride, int box_rows = kTile) {
+// (also used by the band SDDMM / SpMM kernels in ops_band.cu)
+bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_rows,
+              int64_t d, int64_t stride, int box_rows = kTile) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)stride, (cuuint64_t)(n_rows / stride),

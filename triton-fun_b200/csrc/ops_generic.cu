@@ -133,6 +133,78 @@ softmax_rows_vec_kernel(const T* __restrict__ s, T* __restrict__ p, const float*
     }
 }
 
+// Rows of at most one 16-byte vector per lane (trailing_dim <= 32 * V): a warp takes R rows at a
+// time and issues all their loads before the first reduction, so that enough bytes are in flight to
+// keep HBM busy (one row per warp leaves the warp waiting on a single 512-byte request).
+template <typename T, int R>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+softmax_rows_short_kernel(const T* __restrict__ s, T* __restrict__ p, const float* __restrict__ nnzs,
+                          int64_t total_rows, int64_t n_rows, int trailing, float scale_log2e) {
+    constexpr int V = DT<T>::kVec;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t grow0 = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * R;
+    if (grow0 >= total_rows) return;
+    const int e0 = lane * V;
+    float vals[R][V];
+    int nnz[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int64_t grow = grow0 + r;
+        nnz[r] = 0;
+        if (grow < total_rows) {
+            int n = (int)rintf(__ldg(nnzs + grow % n_rows));
+            nnz[r] = n < 0 ? 0 : (n > trailing ? trailing : n);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (e0 < nnz[r]) {
+            load16_as_float(s + (grow0 + r) * trailing + e0, vals[r]);
+        } else {
+#pragma unroll
+            for (int t = 0; t < V; ++t) vals[r][t] = 0.f;
+        }
+    }
+    float m[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        m[r] = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < V; ++t) {
+            vals[r][t] = (e0 + t < nnz[r]) ? vals[r][t] * scale_log2e : -INFINITY;
+            m[r] = fmaxf(m[r], vals[r][t]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < R; ++r) m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], o));
+    float sum[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        sum[r] = 0.f;
+#pragma unroll
+        for (int t = 0; t < V; ++t) {
+            const float e = (vals[r][t] == -INFINITY) ? 0.f : exp2f(vals[r][t] - m[r]);
+            vals[r][t] = e;
+            sum[r] += e;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < R; ++r) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], o);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (grow0 + r < total_rows && e0 < trailing) {
+            const float inv = sum[r] > 0.f ? 1.f / sum[r] : 0.f;
+#pragma unroll
+            for (int t = 0; t < V; ++t) vals[r][t] *= inv;
+            store16_from_float(p + (grow0 + r) * trailing + e0, vals[r]);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 softmax_rows_loop_kernel(const T* __restrict__ s, T* __restrict__ p,
@@ -337,7 +409,12 @@ static int32_t softmax_t(const void* s, void* p, const float* nnzs, int64_t bh, 
     constexpr int V = DT<T>::kVec;
     const bool vec = (trailing % V == 0) && trailing <= 32 * V * kSoftmaxMaxVec && aligned16(s) &&
                      aligned16(p);
-    if (vec)
+    if (vec && trailing <= 32 * V) {
+        constexpr int R = 4;
+        const unsigned grid_r = (unsigned)((total + (int64_t)kWarpsPerBlock * R - 1) / (kWarpsPerBlock * R));
+        softmax_rows_short_kernel<T, R><<<grid_r, kWarpsPerBlock * 32, 0, st>>>(
+            (const T*)s, (T*)p, nnzs, total, n_rows, (int)trailing, scale * kLog2e);
+    } else if (vec)
         softmax_rows_vec_kernel<T><<<grid, kWarpsPerBlock * 32, 0, st>>>(
             (const T*)s, (T*)p, nnzs, total, n_rows, (int)trailing, scale * kLog2e);
     else
