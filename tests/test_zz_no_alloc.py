@@ -20,15 +20,16 @@ pytestmark = pytest.mark.gpu
 
 
 def _three_entry_points(n, q, kt, v, acsr, scale):
-    """Reference result from the existing entry points with caller-owned S and P buffers."""
+    """Reference result from the existing entry points (splat_sddmm, splat_softmax, splat_spmm: the
+    kernels the no-allocation variant chains) with caller-owned S and P buffers."""
     B, H, L, d = q.shape
     T = acsr[5]
     s = torch.empty((B, H, L, T), dtype=q.dtype, device=q.device)
     p = torch.empty_like(s)
     o = torch.empty_like(q)
-    n.sddmm(q, kt, s, acsr[2], acsr[3], acsr[4], T)
+    n.sddmm(q, kt, s, acsr[2], acsr[3], acsr[4], T, n.PATH_GENERIC)
     n.softmax(s, p, acsr[4], T, scale)
-    n.spmm(p, v, o, acsr[2], acsr[3], acsr[4], T)
+    n.spmm(p, v, o, acsr[2], acsr[3], acsr[4], T, n.PATH_GENERIC)
     return o
 
 

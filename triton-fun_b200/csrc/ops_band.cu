@@ -89,6 +89,9 @@ struct Control {
     int32_t abort_at_entry;
     int32_t red_lo[4];
     int32_t red_hi[4];
+    // per row and step: where its run of the sparse operand starts in global memory and which of
+    // the step's 64 columns it covers; written by the row's own lane, read by the whole warp
+    struct RowRun { unsigned long long ptr; int lo; int hi; } run[kTile];
 };
 
 // Per-row band metadata of the 128 rows of a tile, and the tile's step range [klo, khi).
@@ -280,16 +283,23 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             __syncwarp();
             const int c0 = k * kStep;
+            {   // this lane's row: destination of column c0 and the valid columns of the step
+                const int64_t real = (int64_t)(u0 + warp * 32 + lane) * p.stride + res;
+                Control::RowRun rrn;
+                rrn.ptr = reinterpret_cast<unsigned long long>(out + (row0 + real) * p.trailing_dim + (c0 - me.a));
+                rrn.lo = me.n > 0 ? max(me.a - c0, 0) : 0;
+                rrn.hi = me.n > 0 ? min(me.a + me.n - c0, kStep) : 0;
+                ctrl->run[warp * 32 + lane] = rrn;
+            }
+            __syncwarp();
+#pragma unroll 8
             for (int rr = 0; rr < 32; ++rr) {
-                const int a = __shfl_sync(0xffffffffu, me.a, rr), n = __shfl_sync(0xffffffffu, me.n, rr);
-                const int v_lo = max(a - c0, 0), v_hi = min(a + n - c0, kStep);   // n = 0: empty
-                if (n == 0 || v_lo >= v_hi) continue;                              // warp-uniform
-                const int64_t real = (int64_t)(u0 + warp * 32 + rr) * p.stride + res;
-                T* dst = out + (row0 + real) * p.trailing_dim + (c0 - a);
+                const Control::RowRun rrn = ctrl->run[warp * 32 + rr];   // broadcast load
+                T* dst = reinterpret_cast<T*>(rrn.ptr);
                 const T* src = reinterpret_cast<const T*>(my_stage + rr * kStagePitch);
 #pragma unroll
                 for (int e = lane; e < kStep; e += 32)
-                    if (e >= v_lo && e < v_hi) dst[e] = src[e];
+                    if (e >= rrn.lo && e < rrn.hi) dst[e] = src[e];
             }
             __syncwarp();   // staging is rewritten in the next step
         }
@@ -466,18 +476,38 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
             }
             uint8_t* tile = s_p + b * L::kPBytes;
             const int c0 = k * kStep;
-            for (int rr = 0; rr < 32; ++rr) {
-                const int a = __shfl_sync(0xffffffffu, me.a, rr), n = __shfl_sync(0xffffffffu, me.n, rr);
-                const int v_lo = a - c0, v_hi = n > 0 ? a + n - c0 : INT_MIN;
-                const int r = warp * 32 + rr;
-                const int64_t real = (int64_t)(u0 + r) * p.stride + res;
-                const T* src = pin + (row0 + real) * p.trailing_dim + (c0 - a);
+            {   // this lane's row: source of column c0 and the valid columns of the step
+                const int64_t real = (int64_t)(u0 + warp * 32 + lane) * p.stride + res;
+                Control::RowRun rrn;
+                rrn.ptr = reinterpret_cast<unsigned long long>(pin + (row0 + real) * p.trailing_dim + (c0 - me.a));
+                rrn.lo = me.n > 0 ? max(me.a - c0, 0) : 0;
+                rrn.hi = me.n > 0 ? min(me.a + me.n - c0, kStep) : 0;
+                __syncwarp();   // the previous step's reads of run[] are done
+                ctrl->run[warp * 32 + lane] = rrn;
+            }
+            __syncwarp();
+            // eight rows at a time: all their loads are issued before the first store
+            for (int rr0 = 0; rr0 < 32; rr0 += 8) {
+                T vals[8][2];
 #pragma unroll
-                for (int e = lane; e < kStep; e += 32) {
-                    T v = from_f<T>(0.f);
-                    if (e >= v_lo && e < v_hi) v = src[e];
-                    // 128-byte-swizzled K-major tile: 16-byte chunk index XOR row mod 8
-                    *reinterpret_cast<T*>(tile + r * 128 + ((((e >> 3) ^ (r & 7))) << 4) + (e & 7) * 2) = v;
+                for (int i = 0; i < 8; ++i) {
+                    const Control::RowRun rrn = ctrl->run[warp * 32 + rr0 + i];   // broadcast load
+                    const T* src = reinterpret_cast<const T*>(rrn.ptr);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int e = lane + 32 * j;
+                        vals[i][j] = (e >= rrn.lo && e < rrn.hi) ? src[e] : from_f<T>(0.f);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = warp * 32 + rr0 + i;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int e = lane + 32 * j;
+                        // 128-byte-swizzled K-major tile: 16-byte chunk index XOR row mod 8
+                        *reinterpret_cast<T*>(tile + r * 128 + ((((e >> 3) ^ (r & 7))) << 4) + (e & 7) * 2) = vals[i][j];
+                    }
                 }
             }
             fence_proxy_async_smem();
