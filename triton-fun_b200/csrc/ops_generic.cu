@@ -147,12 +147,15 @@ softmax_rows_short_kernel(const T* __restrict__ s, T* __restrict__ p, const floa
     const int e0 = lane * V;
     float vals[R][V];
     int nnz[R];
+    const int64_t in_head0 = grow0 % n_rows;   // one 64-bit division per warp
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int64_t grow = grow0 + r;
         nnz[r] = 0;
         if (grow < total_rows) {
-            int n = (int)rintf(__ldg(nnzs + grow % n_rows));
+            int64_t in_head = in_head0 + r;
+            while (in_head >= n_rows) in_head -= n_rows;
+            int n = (int)rintf(__ldg(nnzs + in_head));
             nnz[r] = n < 0 ? 0 : (n > trailing ? trailing : n);
         }
     }
@@ -410,7 +413,7 @@ static int32_t softmax_t(const void* s, void* p, const float* nnzs, int64_t bh, 
     const bool vec = (trailing % V == 0) && trailing <= 32 * V * kSoftmaxMaxVec && aligned16(s) &&
                      aligned16(p);
     if (vec && trailing <= 32 * V) {
-        constexpr int R = 4;
+        constexpr int R = 2;
         const unsigned grid_r = (unsigned)((total + (int64_t)kWarpsPerBlock * R - 1) / (kWarpsPerBlock * R));
         softmax_rows_short_kernel<T, R><<<grid_r, kWarpsPerBlock * 32, 0, st>>>(
             (const T*)s, (T*)p, nnzs, total, n_rows, (int)trailing, scale * kLog2e);
