@@ -5,7 +5,7 @@
 // the tensor cores only have to keep up with that stream.
 //
 //   sddmm_band_kernel   S[i, j'] = Q[i] . K[start_i + j' stride]   (SPLAT/r_sddmm.py:16-114)
-//       one CTA = one 128-row Q tile of one (bh, residue class); K travels in 64-key ring items;
+//       one CTA = one 128-row Q tile of one (bh, residue class), eight row warps; K travels in 64-key ring items;
 //       S(k) = Q K(k)^T (8 x tcgen05.mma 128x64x16) lands in one of two 64-column buffers; the
 //       store warps read their row's 64 scores, convert, transpose through shared memory and write
 //       each row's run of the band into the sparse layout with coalesced stores.
@@ -37,7 +37,10 @@ constexpr int kTile = 128;
 constexpr int kStep = 64;
 constexpr int kSubBytes = kTile * 128;          // 128 rows x 128 bytes
 constexpr int kStepBytesPerSub = kStep * 128;   // 64 keys x 128 bytes
-constexpr int kThreads = 192;                   // warps 0-3 rows, 4 TMA producer, 5 MMA issuer
+constexpr int kRowWarps = 8;                    // row warp (q, h) = (warp & 3, warp >> 2): rows 32q .. 32q+31, half h of the work
+constexpr int kThreads = 320;                   // warps 0-7 rows, 8 TMA producer, 9 MMA issuer
+constexpr int kTmaWarp = 8;
+constexpr int kMmaWarp = 9;
 constexpr int kStages = 3;                     // ring depth that lets two CTAs share an SM at d = 128
 constexpr int kStagePitch = 144;                // bytes per staged row: 128 + 16, conflict-free 16-byte stores
 enum : int { kErrQ = 11, kErrFull = 12, kErrEmpty = 13, kErrReady = 14, kErrFree = 15 };
@@ -91,7 +94,7 @@ struct Control {
     int32_t red_hi[4];
     // per row and step: where its run of the sparse operand starts in global memory and which of
     // the step's 64 columns it covers; written by the row's own lane, read by the whole warp
-    struct RowRun { unsigned long long ptr; int lo; int hi; } run[kTile];
+    struct RowRun { unsigned long long ptr; int lo; int hi; } run[kRowWarps][32];   // one copy per row warp
 };
 
 // Per-row band metadata of the 128 rows of a tile, and the tile's step range [klo, khi).
@@ -130,7 +133,7 @@ template <int D> struct SddmmLayout {
 };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const Params p) {
     using L = SddmmLayout<D>;
@@ -149,7 +152,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int64_t bh = blockIdx.z;
     const int u0 = blockIdx.x * kTile;
 
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tmem_alloc(&ctrl->tmem_base, kTmemCols);
         tmem_relinquish();
     }
@@ -161,27 +164,27 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctrl->ready[b], 1);
-            mbar_init(&ctrl->freed[b], 4);
+            mbar_init(&ctrl->freed[b], kRowWarps);
         }
         mbar_init(&ctrl->drain, 1);
         mbar_fence_init();
         ctrl->abort_at_entry = *status;
     }
     RowInfo me{0, 0, 0, 0};
-    if (warp < 4) {
-        me = load_row(p, u0 + warp * 32 + lane, res);
+    if (warp < kRowWarps) {
+        me = load_row(p, u0 + (warp & 3) * 32 + lane, res);
         int lo = me.n > 0 ? me.a / kStep : INT_MAX;
         int hi = me.n > 0 ? (me.a + me.n + kStep - 1) / kStep : 0;
         lo = warp_min_i(lo);
         hi = warp_max_i(hi);
-        if (lane == 0) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
+        if (lane == 0 && warp < 4) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
     if (ctrl->abort_at_entry != 0) {
-        if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+        if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
         return;
     }
     int klo = INT_MAX, khi = 0;
@@ -193,7 +196,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (klo >= khi) { klo = 0; khi = 0; }
     const int steps = khi - klo;
 
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && steps > 0) {
             tma_prefetch_desc(&tm_q);
@@ -218,7 +221,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     wait_quiet(&ctrl->full[i % kStages], (uint32_t)(i / kStages) & 1u);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
@@ -251,9 +254,12 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else {
         // ------------------------------------------------------------------ store warps
-        const uint32_t s_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        // Warp (q, h): rows 32q .. 32q+31 (its tensor-memory lanes), columns [32h, 32h + 32) of
+        // every 64-column step.  Each warp stages and writes out only what its own lanes read.
+        const int q = warp & 3, h = warp >> 2;
+        const uint32_t s_addr = tmem_base + ((uint32_t)(q * 32) << 16) + h * 32;
         T* out = reinterpret_cast<T*>(p.sparse);
-        uint8_t* my_stage = s_stage + (warp * 32) * kStagePitch;
+        uint8_t* my_stage = s_stage + (q * 32) * kStagePitch + h * 64;   // this warp's half of the 128-byte rows
         const int64_t row0 = bh * p.n_rows;   // + real row
         uint32_t phase[2] = {0, 0};
         bool ok = true;
@@ -264,16 +270,15 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (!ok) break;
             phase[b] ^= 1u;
             tc_fence_after_sync();
-            uint32_t r[kStep];
+            uint32_t r[32];
             tmem_ld32(s_addr + b * kStep, r);
-            tmem_ld32(s_addr + b * kStep + 32, r + 32);
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->freed[b]);   // the buffer may take the scores of step k + 2
             // own row -> staging (16-bit), then row by row out of staging with coalesced stores
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint4 v4;
                 v4.x = pack2<T>(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
                 v4.y = pack2<T>(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
@@ -281,35 +286,44 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 v4.w = pack2<T>(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
                 *reinterpret_cast<uint4*>(my_stage + lane * kStagePitch + c * 16) = v4;
             }
-            __syncwarp();
-            const int c0 = k * kStep;
-            {   // this lane's row: destination of column c0 and the valid columns of the step
-                const int64_t real = (int64_t)(u0 + warp * 32 + lane) * p.stride + res;
+            const int c0 = k * kStep + h * 32;   // first column of this warp's half
+            {   // this lane's row: destination of column c0 and the valid columns of the half
+                const int64_t real = (int64_t)(u0 + q * 32 + lane) * p.stride + res;
                 Control::RowRun rrn;
                 rrn.ptr = reinterpret_cast<unsigned long long>(out + (row0 + real) * p.trailing_dim + (c0 - me.a));
                 rrn.lo = me.n > 0 ? max(me.a - c0, 0) : 0;
-                rrn.hi = me.n > 0 ? min(me.a + me.n - c0, kStep) : 0;
-                ctrl->run[warp * 32 + lane] = rrn;
+                rrn.hi = me.n > 0 ? min(me.a + me.n - c0, 32) : 0;
+                ctrl->run[warp][lane] = rrn;
             }
             __syncwarp();
-#pragma unroll 8
-            for (int rr = 0; rr < 32; ++rr) {
-                const Control::RowRun rrn = ctrl->run[warp * 32 + rr];   // broadcast load
-                T* dst = reinterpret_cast<T*>(rrn.ptr);
-                const T* src = reinterpret_cast<const T*>(my_stage + rr * kStagePitch);
+            // eight rows at a time, loads first: the compiler cannot move a shared-memory load above
+            // a store through a pointer it knows nothing about, and one row per round trip is slow
+            for (int rr0 = 0; rr0 < 32; rr0 += 8) {
+                Control::RowRun d[8];
+                T vals[8];
 #pragma unroll
-                for (int e = lane; e < kStep; e += 32)
-                    if (e >= rrn.lo && e < rrn.hi) dst[e] = src[e];
+                for (int i = 0; i < 8; ++i) d[i] = ctrl->run[warp][rr0 + i];   // broadcast loads
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    vals[i] = reinterpret_cast<const T*>(my_stage + (rr0 + i) * kStagePitch)[lane];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (lane >= d[i].lo && lane < d[i].hi) reinterpret_cast<T*>(d[i].ptr)[lane] = vals[i];
             }
-            __syncwarp();   // staging is rewritten in the next step
+            __syncwarp();   // staging and run[] are rewritten in the next step
         }
-        // padding slots, rows with one non-zero (a dot product by hand) and rows with none
+        // padding slots, rows with one non-zero (a dot product by hand) and rows with none:
+        // even rows by the h = 0 warp, odd rows by the h = 1 warp
         {
             const T* qg = reinterpret_cast<const T*>(p.q);
             const T* kg = reinterpret_cast<const T*>(p.kv);
-            for (int rr = 0; rr < 32; ++rr) {
-                const int u = u0 + warp * 32 + rr;
-                if (u >= p.rows_v) break;
+            // most rows are full (nnz == trailing_dim, no padding): visit only the others
+            const bool mine = (lane & 1) == h && u0 + q * 32 + lane < p.rows_v;
+            unsigned todo = __ballot_sync(0xffffffffu, mine && (me.nnz < p.trailing_dim || me.nnz == 1));
+            while (todo) {
+                const int rr = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const int u = u0 + q * 32 + rr;
                 const int nnz = __shfl_sync(0xffffffffu, me.nnz, rr);
                 const int start = __shfl_sync(0xffffffffu, me.start, rr);
                 const int64_t real = (int64_t)u * p.stride + res;
@@ -329,7 +343,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -370,7 +384,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
     const int64_t bh = blockIdx.z;
     const int u0 = blockIdx.x * kTile;
 
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tmem_alloc(&ctrl->tmem_base, kTmemCols);
         tmem_relinquish();
     }
@@ -380,7 +394,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
             mbar_init(&ctrl->empty[i], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&ctrl->ready[b], 4);
+            mbar_init(&ctrl->ready[b], kRowWarps);
             mbar_init(&ctrl->freed[b], 1);
         }
         mbar_init(&ctrl->drain, 1);
@@ -388,20 +402,20 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
         ctrl->abort_at_entry = *status;
     }
     RowInfo me{0, 0, 0, 0};
-    if (warp < 4) {
-        me = load_row(p, u0 + warp * 32 + lane, res);
+    if (warp < kRowWarps) {
+        me = load_row(p, u0 + (warp & 3) * 32 + lane, res);
         int lo = me.n > 0 ? me.a / kStep : INT_MAX;
         int hi = me.n > 0 ? (me.a + me.n + kStep - 1) / kStep : 0;
         lo = warp_min_i(lo);
         hi = warp_max_i(hi);
-        if (lane == 0) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
+        if (lane == 0 && warp < 4) { ctrl->red_lo[warp] = lo; ctrl->red_hi[warp] = hi; }
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
     if (ctrl->abort_at_entry != 0) {
-        if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+        if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
         return;
     }
     int klo = INT_MAX, khi = 0;
@@ -413,7 +427,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
     if (klo >= khi) { klo = 0; khi = 0; }
     const int steps = khi - klo;
 
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer (V)
         if (lane == 0 && steps > 0) {
             tma_prefetch_desc(&tm_v);
@@ -432,7 +446,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
                 for (int i = max(0, item - kStages); i < item; ++i)
                     wait_quiet(&ctrl->full[i % kStages], (uint32_t)(i / kStages) & 1u);
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
@@ -462,6 +476,9 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
         }
     } else {
         // ------------------------------------------------------------------ P loaders + epilogue
+        // Warp (q, h): the loader of rows 32q + 16h .. + 15 (all 64 columns of a step), and in the
+        // epilogue the 32-column chunks ch with ch mod 2 == h of rows 32q .. 32q+31.
+        const int q = warp & 3, h = warp >> 2;
         const T* pin = reinterpret_cast<const T*>(p.sparse);
         const int64_t row0 = bh * p.n_rows;
         uint32_t free_phase[2] = {0, 0};
@@ -477,21 +494,21 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
             uint8_t* tile = s_p + b * L::kPBytes;
             const int c0 = k * kStep;
             {   // this lane's row: source of column c0 and the valid columns of the step
-                const int64_t real = (int64_t)(u0 + warp * 32 + lane) * p.stride + res;
+                const int64_t real = (int64_t)(u0 + q * 32 + lane) * p.stride + res;
                 Control::RowRun rrn;
                 rrn.ptr = reinterpret_cast<unsigned long long>(pin + (row0 + real) * p.trailing_dim + (c0 - me.a));
                 rrn.lo = me.n > 0 ? max(me.a - c0, 0) : 0;
                 rrn.hi = me.n > 0 ? min(me.a + me.n - c0, kStep) : 0;
                 __syncwarp();   // the previous step's reads of run[] are done
-                ctrl->run[warp * 32 + lane] = rrn;
+                ctrl->run[warp][lane] = rrn;
             }
             __syncwarp();
             // eight rows at a time: all their loads are issued before the first store
-            for (int rr0 = 0; rr0 < 32; rr0 += 8) {
+            for (int rr0 = h * 16; rr0 < h * 16 + 16; rr0 += 8) {
                 T vals[8][2];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const Control::RowRun rrn = ctrl->run[warp * 32 + rr0 + i];   // broadcast load
+                    const Control::RowRun rrn = ctrl->run[warp][rr0 + i];   // broadcast load
                     const T* src = reinterpret_cast<const T*>(rrn.ptr);
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
@@ -501,7 +518,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int r = warp * 32 + rr0 + i;
+                    const int r = q * 32 + rr0 + i;
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int e = lane + 32 * j;
@@ -522,15 +539,16 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
         }
         // epilogue: O for band rows, P[i,0] * V[start] for single-element rows, zero otherwise,
         // staged in the (now free) P tiles in the swizzled layout, one TMA store per 64 columns
-        const uint32_t o_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        const int t = warp * 32 + lane;
+        const uint32_t o_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const int t = q * 32 + lane;
         const int64_t real = (int64_t)(u0 + t) * p.stride + res;
         const T* vrow = reinterpret_cast<const T*>(p.kv) + (row0 + me.start) * D;
         float p0 = 0.f;
         if (me.nnz == 1) p0 = to_f<T>(pin[(row0 + real) * p.trailing_dim]);
         uint32_t r[32];
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int c = 0; c < D / 64; ++c) {
+            const int ch = 2 * c + h;   // this warp's 32-column chunks
             if (have_o && ok) {
                 tmem_ld32(o_addr + ch * 32, r);
                 tmem_ld_wait();
@@ -555,7 +573,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
                 *reinterpret_cast<uint4*>(srow + ((((ch & 1) * 4 + q4) ^ (t & 7)) << 4)) = outv[q4];
         }
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four row warps, unconditionally
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight row warps, unconditionally
         if (threadIdx.x == 0) {
             for (int sub = 0; sub < L::kSub; ++sub)
                 tma_store_4d(&tm_o, smem + sub * kSubBytes, sub * 64, res, u0, (int)bh);
@@ -565,7 +583,7 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);

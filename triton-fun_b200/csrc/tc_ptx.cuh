@@ -45,16 +45,23 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  "r"(bytes)
                  : "memory");
 }
+// A waiting thread is parked by the hardware until the phase completes or this many nanoseconds
+// have passed, instead of re-issuing the test: polling warps otherwise take issue slots from the
+// warps that do the arithmetic on the same scheduler.
+#ifndef SPLAT_SUSPEND_HINT_NS
+#define SPLAT_SUSPEND_HINT_NS 2000
+#endif
+constexpr uint32_t kSuspendHintNs = SPLAT_SUSPEND_HINT_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
@@ -70,6 +77,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     const long long t0 = clock64();
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
+#ifdef SPLAT_WAIT_SLEEP_NS
+        __nanosleep(SPLAT_WAIT_SLEEP_NS);
+#endif
         if ((++polls & 0x3ffu) == 0) {
             if (*status_word != 0) return false;
             if (clock64() - t0 > limit_cycles) {
