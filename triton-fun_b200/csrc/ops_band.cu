@@ -366,7 +366,7 @@ template <int D> struct SpmmLayout {
 };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                  const Params p) {
     using L = SpmmLayout<D>;
