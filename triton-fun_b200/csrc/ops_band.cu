@@ -46,6 +46,9 @@ constexpr int kStagePitch = 144;                // bytes per staged row: 128 + 1
 enum : int { kErrQ = 11, kErrFull = 12, kErrEmpty = 13, kErrReady = 14, kErrFree = 15 };
 
 struct Params {
+#ifdef SPLAT_OPS_TRACE
+    long long* trace;
+#endif
     const float* lin;
     const float* tr;
     const float* nnzs;
@@ -57,7 +60,17 @@ struct Params {
     int rows_v;          // L / stride
     int stride;
     int trailing_dim;
+    int direct;          // sddmm: S is 16-byte aligned, full runs may be stored straight from registers
 };
+
+#ifdef SPLAT_OPS_TRACE
+#define OPS_TRACE(tag)                                                                    \
+    do {                                                                                  \
+        if (trace_on && lane == 0 && trace_n < 256) p.trace[trace_role * 256 + trace_n++] = ((long long)(tag) << 48) | (clock64() & 0xffffffffffffLL); \
+    } while (0)
+#else
+#define OPS_TRACE(tag) do { } while (0)
+#endif
 
 __device__ __forceinline__ void wait_quiet(uint64_t* bar, uint32_t parity) {
     const long long t0 = clock64();
@@ -119,6 +132,60 @@ __device__ __forceinline__ RowInfo load_row(const Params& p, int u, int res) {
     return r;
 }
 
+// Stores 32 consecutive 16-bit elements (w[j] = elements 2j, 2j+1) at element offset g0 of a
+// 16-byte-aligned array, from one thread, with the widest aligned stores the offset allows: the
+// data is shifted in registers by g0 mod 8 elements (a 16-bit funnel shift for the odd part, two
+// rounds of selects for the word part, no divergence), the three middle 16-byte chunks go out
+// whole, the partial first and last chunks in 8/4/2-byte pieces.  Ten store instructions per warp
+// for 2 KB instead of one shared-memory load and one 2-byte store per element.
+__device__ __forceinline__ void store_run_shifted(uint16_t* base, long long g0, const uint32_t (&w)[16]) {
+    const int sft = (int)(g0 & 7);
+    uint16_t* gp = base + (g0 - sft);   // 16-byte aligned
+    const bool odd = sft & 1;
+    uint32_t v[20];
+#pragma unroll
+    for (int j = 0; j < 17; ++j) {
+        const uint32_t lo = j > 0 ? w[j - 1] : 0u, hi = j < 16 ? w[j] : 0u;
+        v[j] = odd ? __funnelshift_l(lo, hi, 16) : hi;
+    }
+    v[17] = v[18] = v[19] = 0u;
+    if (sft & 2) {
+#pragma unroll
+        for (int j = 19; j >= 1; --j) v[j] = v[j - 1];
+        v[0] = 0u;
+    }
+    if (sft & 4) {
+#pragma unroll
+        for (int j = 19; j >= 2; --j) v[j] = v[j - 2];
+        v[0] = v[1] = 0u;
+    }
+    // whole chunks 1..3 (relative elements 8..31 are always inside [sft, sft + 32))
+#pragma unroll
+    for (int c = 1; c < 4; ++c)
+        *reinterpret_cast<uint4*>(gp + 8 * c) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    // first chunk: relative elements [sft, 8)
+    if (sft == 0) {
+        *reinterpret_cast<uint4*>(gp) = make_uint4(v[0], v[1], v[2], v[3]);
+    } else {
+        if (odd) {   // element sft: upper half of word sft >> 1
+            const uint32_t wv = sft < 4 ? (sft < 2 ? v[0] : v[1]) : (sft < 6 ? v[2] : v[3]);
+            gp[sft] = (uint16_t)(wv >> 16);
+        }
+        const int t1 = sft + (sft & 1);           // even, 2..8
+        if (t1 & 2) *reinterpret_cast<uint32_t*>(gp + t1) = t1 == 2 ? v[1] : v[3];
+        const int t2 = t1 + (t1 & 2);             // 4 or 8
+        if (t2 == 4) *reinterpret_cast<uint2*>(gp + 4) = make_uint2(v[2], v[3]);
+    }
+    // last chunk: relative elements [32, 32 + sft)
+    if (sft & 4) *reinterpret_cast<uint2*>(gp + 32) = make_uint2(v[16], v[17]);
+    if (sft & 2) *reinterpret_cast<uint32_t*>(gp + 32 + (sft & 4)) = (sft & 4) ? v[18] : v[16];
+    if (odd) {
+        const int e = sft & 6;                    // 0, 2, 4, 6: lower half of word 16 + e / 2
+        const uint32_t wv = e < 4 ? (e < 2 ? v[16] : v[17]) : (e < 6 ? v[18] : v[19]);
+        gp[32 + e] = (uint16_t)(wv & 0xffffu);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // SDDMM
 // ---------------------------------------------------------------------------------------------
@@ -151,6 +218,12 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int res = blockIdx.y;
     const int64_t bh = blockIdx.z;
     const int u0 = blockIdx.x * kTile;
+#ifdef SPLAT_OPS_TRACE
+    const bool trace_on = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.z == gridDim.z / 2 && (warp == 0 || warp == kMmaWarp);
+    const int trace_role = warp == 0 ? 0 : 1;
+    int trace_n = 0;
+    OPS_TRACE(1);
+#endif
 
     if (warp == kMmaWarp) {
         tmem_alloc(&ctrl->tmem_base, kTmemCols);
@@ -238,6 +311,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 if (!ok) break;
                 tc_fence_after_sync();
+                OPS_TRACE(20);
                 const uint32_t b_base = ring_addr + (item % kStages) * L::kItemBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
@@ -247,6 +321,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                            idesc, kk > 0);
                 mma_commit(&ctrl->empty[item % kStages]);
                 mma_commit(&ctrl->ready[b]);
+                OPS_TRACE(21);
             }
             // let the tensor pipe drain before tensor memory is released
             mma_commit(&ctrl->drain);
@@ -265,17 +340,33 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         bool ok = true;
         for (int k = klo; k < khi; ++k) {
             const int b = k & 1;
+            OPS_TRACE(4);
             ok = mbar_wait(&ctrl->ready[b], phase[b], status, kErrReady);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             phase[b] ^= 1u;
             tc_fence_after_sync();
+            OPS_TRACE(5);
             uint32_t r[32];
             tmem_ld32(s_addr + b * kStep, r);
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->freed[b]);   // the buffer may take the scores of step k + 2
+            OPS_TRACE(6);
+            const int c0 = k * kStep + h * 32;   // first column of this warp's half
+            // Fast path, every row of the warp has all 32 columns of this half inside its band:
+            // each thread writes its own run straight from registers.
+            if (p.direct && __all_sync(0xffffffffu, me.n > 0 && me.a <= c0 && me.a + me.n >= c0 + 32)) {
+                uint32_t w[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    w[j] = pack2<T>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                const int64_t real = (int64_t)(u0 + q * 32 + lane) * p.stride + res;
+                store_run_shifted(reinterpret_cast<uint16_t*>(out),
+                                  (long long)((row0 + real) * p.trailing_dim + (c0 - me.a)), w);
+                continue;
+            }
             // own row -> staging (16-bit), then row by row out of staging with coalesced stores
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -286,7 +377,6 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 v4.w = pack2<T>(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
                 *reinterpret_cast<uint4*>(my_stage + lane * kStagePitch + c * 16) = v4;
             }
-            const int c0 = k * kStep + h * 32;   // first column of this warp's half
             {   // this lane's row: destination of column c0 and the valid columns of the half
                 const int64_t real = (int64_t)(u0 + q * 32 + lane) * p.stride + res;
                 Control::RowRun rrn;
@@ -296,6 +386,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 ctrl->run[warp][lane] = rrn;
             }
             __syncwarp();
+            OPS_TRACE(7);
             // eight rows at a time, loads first: the compiler cannot move a shared-memory load above
             // a store through a pointer it knows nothing about, and one row per round trip is slow
             for (int rr0 = 0; rr0 < 32; rr0 += 8) {
@@ -311,7 +402,9 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     if (lane >= d[i].lo && lane < d[i].hi) reinterpret_cast<T*>(d[i].ptr)[lane] = vals[i];
             }
             __syncwarp();   // staging and run[] are rewritten in the next step
+            OPS_TRACE(8);
         }
+        OPS_TRACE(9);
         // padding slots, rows with one non-zero (a dot product by hand) and rows with none:
         // even rows by the h = 0 warp, odd rows by the h = 1 warp
         {
@@ -340,6 +433,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
         (void)ok;
+        OPS_TRACE(10);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -616,6 +710,9 @@ static int32_t launch_spmm(const CUtensorMap& mv, const CUtensorMap& mo, const P
     return launch_status();
 }
 
+#ifdef SPLAT_OPS_TRACE
+static long long* g_trace = nullptr;
+#endif
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Checks shared by both operators; fills stride.  plan as written by splat_acsr_classify:
@@ -662,9 +759,13 @@ extern "C" int32_t splat_sddmm_band(const void* q, const void* k, int64_t k_stri
         !make_map(&mk, k, dtype, bh, n_rows, d, stride, ops::kStep))
         return SPLAT_ERR_DRIVER;
     ops::Params prm;
+#ifdef SPLAT_OPS_TRACE
+    prm.trace = ops::g_trace;
+#endif
     prm.lin = sTod_lin; prm.tr = sTod_tr; prm.nnzs = nnzs; prm.q = q; prm.kv = k; prm.sparse = s_out;
     prm.status = status_word; prm.n_rows = n_rows; prm.rows_v = (int)(n_rows / stride);
     prm.stride = (int)stride; prm.trailing_dim = (int)trailing_dim;
+    prm.direct = ops::aligned16(s_out) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == SPLAT_BF16)
         return d == 128 ? ops::launch_sddmm<__nv_bfloat16, 128>(mq, mk, prm, bh, st)
@@ -688,10 +789,14 @@ extern "C" int32_t splat_spmm_band(const void* p, const void* v, void* o, const 
         !make_map(&mo, o, dtype, bh, n_rows, d, stride, ops::kTile))
         return SPLAT_ERR_DRIVER;
     ops::Params prm;
+#ifdef SPLAT_OPS_TRACE
+    prm.trace = nullptr;
+#endif
     prm.lin = sTod_lin; prm.tr = sTod_tr; prm.nnzs = nnzs; prm.q = nullptr; prm.kv = v;
     prm.sparse = const_cast<void*>(p);
     prm.status = status_word; prm.n_rows = n_rows; prm.rows_v = (int)(n_rows / stride);
     prm.stride = (int)stride; prm.trailing_dim = (int)trailing_dim;
+    prm.direct = 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == SPLAT_BF16)
         return d == 128 ? ops::launch_spmm<__nv_bfloat16, 128>(mv, mo, prm, bh, st)
@@ -699,3 +804,9 @@ extern "C" int32_t splat_spmm_band(const void* p, const void* v, void* o, const 
     return d == 128 ? ops::launch_spmm<__half, 128>(mv, mo, prm, bh, st)
                     : ops::launch_spmm<__half, 64>(mv, mo, prm, bh, st);
 }
+
+#ifdef SPLAT_OPS_TRACE
+extern "C" void splat_debug_set_ops_trace(void* device_buffer_2x256_i64) {
+    splat::band::ops::g_trace = reinterpret_cast<long long*>(device_buffer_2x256_i64);
+}
+#endif
