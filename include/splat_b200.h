@@ -132,7 +132,8 @@ int32_t splat_sddmm(const void* q, const void* k, int64_t k_stride_bh, int64_t k
                     const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                     int64_t trailing_dim, int32_t dtype, void* stream);
 
-/* P[bh,i,j] = softmax_j(scale * S[bh,i,j]) over j < nnz_i, for ALL rows.
+/* P[bh,i,j] = softmax_j(scale * S[bh,i,j]) over j < nnz_i, for ALL rows.  s_in == p_out (in place)
+ * is allowed.
  * Stands in for rsoftmax_launcher -> r_softmax_1d_kernel (SPLAT/r_softmax.py:17-59,126-150);
  * the reference applies no scale (scale = 1). */
 int32_t splat_softmax(const void* s_in, void* p_out, const float* nnzs, int64_t bh, int64_t n_rows,
@@ -151,13 +152,31 @@ int32_t splat_spmm(const void* p, const void* v, void* o, const float* sTod_lin,
  *   plan_i32 .... HOST pointer to a copy of the 8 ints of splat_acsr_classify, or NULL (then only
  *                 the generic kernel can run)
  *   status_word . device int32 the band kernel sets non-zero if one of its bounded waits gives up;
- *                 may be NULL for the generic path.  The caller clears and reads it. */
+ *                 may be NULL for the generic path.  The caller clears and reads it.  WHILE THE WORD
+ *                 IS NON-ZERO EVERY TENSOR-CORE KERNEL THAT IS GIVEN IT RETURNS AT ENTRY WITHOUT
+ *                 WRITING ITS OUTPUT (the entry point still returns SPLAT_OK: nothing is known at
+ *                 enqueue time).  Read the word wherever the stream is synchronised anyway; a
+ *                 non-zero value means the outputs of that launch and of every later one are not
+ *                 valid until the word is cleared.
+ * Under SPLAT_PATH_AUTO a band path that does not apply (shape, pattern, operand alignment, no
+ * tensor-map support in the driver) falls through to the generic kernel. */
 int32_t splat_attention_fused(const void* q, const void* k, int64_t k_stride_bh,
                               int64_t k_stride_col, int64_t k_stride_k, const void* v, void* o,
                               const float* sTod_lin, const float* sTod_tr, const float* nnzs,
                               int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d, float scale,
                               int32_t dtype, int32_t path, const int32_t* plan_i32,
                               int32_t* status_word, void* stream);
+
+/* The same call with one more output: *path_ran (HOST int32, may be NULL) receives SPLAT_PATH_BAND or
+ * SPLAT_PATH_GENERIC according to the kernel that was enqueued (SPLAT_PATH_AUTO: none).  A caller
+ * uses it to know whether status_word can have been touched.  Same reference counterpart as
+ * splat_attention_fused. */
+int32_t splat_attention_fused_ex(const void* q, const void* k, int64_t k_stride_bh,
+                                 int64_t k_stride_col, int64_t k_stride_k, const void* v, void* o,
+                                 const float* sTod_lin, const float* sTod_tr, const float* nnzs,
+                                 int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d, float scale,
+                                 int32_t dtype, int32_t path, const int32_t* plan_i32,
+                                 int32_t* status_word, int32_t* path_ran, void* stream);
 
 /* The three-launch chain (SDDMM, softmax in place, SpMM) for callers that cannot allocate device
  * memory -- code running after its host application froze its memory pool, plug-ins that receive

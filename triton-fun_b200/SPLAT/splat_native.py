@@ -37,6 +37,8 @@ SIGNATURES = {
     "splat_spmm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp],
     "splat_attention_fused": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                               _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
+    "splat_attention_fused_ex": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                 _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp, _vp],
     "splat_sddmm_band": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
                          _i32, _vp, _vp, _vp],
     "splat_spmm_band": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp,
@@ -171,6 +173,7 @@ def classify(sTod_lin: torch.Tensor, sTod_tr: torch.Tensor, nnzs: torch.Tensor) 
 
 
 _STATUS_WORDS: dict = {}
+_STATUS_MIRRORS: dict = {}
 
 
 def status_word(dev: torch.device) -> torch.Tensor:
@@ -183,6 +186,45 @@ def status_word(dev: torch.device) -> torch.Tensor:
     return t
 
 
+def _mirror(dev: torch.device) -> dict:
+    """Pinned host copy of the status word, refreshed after every tensor-core launch by a copy on
+    a side stream, so that the host can look at it without synchronising the device."""
+    key = (dev.type, dev.index)
+    m = _STATUS_MIRRORS.get(key)
+    if m is None:
+        m = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "stream": torch.cuda.Stream(dev),
+             "launched": torch.cuda.Event()}
+        _STATUS_MIRRORS[key] = m
+    return m
+
+
+def _raise_if_gave_up(dev: torch.device) -> None:
+    """Start of every tensor-core launcher: if an earlier launch on this device reported a
+    timed-out wait (the kernels do nothing while the word is set), clear the word and raise
+    instead of silently returning stale outputs.  Costs one host memory read."""
+    m = _STATUS_MIRRORS.get((dev.type, dev.index))
+    if m is None or int(m["host"][0]) == 0:
+        return
+    torch.cuda.synchronize(dev)
+    code = int(status_word(dev).item())
+    status_word(dev).zero_()
+    m["host"].zero_()
+    torch.cuda.synchronize(dev)
+    raise RuntimeError(f"an earlier tensor-core kernel on {dev} gave up on a device-side wait "
+                       f"(code {code}): {status_string(-5)}; its outputs and those of later "
+                       "launches are not valid")
+
+
+def _refresh_mirror(dev: torch.device) -> None:
+    """After a tensor-core launch: copy the status word to its pinned mirror behind the launch, on
+    a side stream, so the launching stream is not delayed."""
+    m = _mirror(dev)
+    m["launched"].record(torch.cuda.current_stream(dev))
+    m["stream"].wait_event(m["launched"])
+    with torch.cuda.stream(m["stream"]):
+        m["host"].copy_(status_word(dev), non_blocking=True)
+
+
 def check_status_word(dev) -> None:
     """Synchronises the device; raises if a band kernel reported a timed-out wait (and clears it)."""
     dev = resolve_device(dev)
@@ -190,6 +232,10 @@ def check_status_word(dev) -> None:
     code = int(w.item())
     if code != 0:
         w.zero_()
+        m = _STATUS_MIRRORS.get((dev.type, dev.index))
+        if m is not None:
+            torch.cuda.synchronize(dev)
+            m["host"].zero_()
         raise RuntimeError(f"band kernel gave up on a device-side wait (code {code}): "
                            f"{status_string(-5)}")
 
@@ -215,7 +261,22 @@ def _contig(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
-ERR_UNSUPPORTED_SHAPE = -6
+ERR_UNSUPPORTED_SHAPE, ERR_MISALIGNED, ERR_DRIVER = -6, -3, -7
+# statuses of a tensor-core entry point that mean "this path does not apply, use the general one"
+_BAND_NOT_APPLICABLE = (ERR_UNSUPPORTED_SHAPE, ERR_MISALIGNED, ERR_DRIVER)
+_warned_cuda_core_16bit = False
+
+
+def _warn_cuda_core_16bit(what: str) -> None:
+    """16-bit operands that land on the CUDA-core kernels run many times slower than on the
+    tensor-core path; say so once."""
+    global _warned_cuda_core_16bit
+    if not _warned_cuda_core_16bit:
+        _warned_cuda_core_16bit = True
+        import warnings
+        warnings.warn(f"{what}: 16-bit operands are running on the CUDA-core kernels (pattern, layout, "
+                      "alignment or head size outside what the tensor-core kernels take); expect a "
+                      "much lower rate", RuntimeWarning, stacklevel=3)
 
 
 def _band_candidate(x: torch.Tensor, path: int) -> bool:
@@ -234,6 +295,7 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = 
     if tuple(output.shape) != (B, H, L, trailing_dim):
         raise ValueError(f"sddmm: output must have shape {(B, H, L, trailing_dim)}")
     if _band_candidate(x, path) and ksk == 1 and ksc == d and ksb == n_cols * d:
+        _raise_if_gave_up(dev)
         plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
         with torch.cuda.device(dev):
             rc = _lib.splat_sddmm_band(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
@@ -241,13 +303,16 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = 
                                        _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, trailing_dim,
                                        dtype_code(x.dtype), ctypes.cast(plan_arr, ctypes.c_void_p),
                                        status_word(dev).data_ptr(), _stream(dev))
-        if rc != ERR_UNSUPPORTED_SHAPE:
+        if rc not in _BAND_NOT_APPLICABLE or path == PATH_BAND:
             check(rc, "splat_sddmm_band")
+            _refresh_mirror(dev)
             if os.environ.get("SPLAT_B200_DEBUG"):
                 check_status_word(dev)
             return
     if path == PATH_BAND:
         raise RuntimeError("sddmm: the band path does not apply to these operands")
+    if x.dtype != torch.float32 and x.numel() > 0:
+        _warn_cuda_core_16bit("sddmm")
     with torch.cuda.device(dev):
         check(_lib.splat_sddmm(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
                                _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
@@ -276,6 +341,7 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
             output.dtype != x.dtype or y.shape[:2] != x.shape[:2]:
         raise ValueError("spmm: inconsistent operand shapes or dtypes")
     if _band_candidate(x, path):
+        _raise_if_gave_up(dev)
         plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
         with torch.cuda.device(dev):
             rc = _lib.splat_spmm_band(x.data_ptr(), y.data_ptr(), output.data_ptr(),
@@ -283,13 +349,16 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
                                       _f32_vec(nnzs, L, "nnzs"), B * H, L, n_cols, d, T,
                                       dtype_code(x.dtype), ctypes.cast(plan_arr, ctypes.c_void_p),
                                       status_word(dev).data_ptr(), _stream(dev))
-        if rc != ERR_UNSUPPORTED_SHAPE:
+        if rc not in _BAND_NOT_APPLICABLE or path == PATH_BAND:
             check(rc, "splat_spmm_band")
+            _refresh_mirror(dev)
             if os.environ.get("SPLAT_B200_DEBUG"):
                 check_status_word(dev)
             return
     if path == PATH_BAND:
         raise RuntimeError("spmm: the band path does not apply to these operands")
+    if x.dtype != torch.float32 and x.numel() > 0:
+        _warn_cuda_core_16bit("spmm")
     with torch.cuda.device(dev):
         check(_lib.splat_spmm(x.data_ptr(), y.data_ptr(), output.data_ptr(),
                               _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
@@ -310,17 +379,25 @@ def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.
             len({q.dtype, kt.dtype, v.dtype, output.dtype}) != 1:
         raise ValueError("attention: inconsistent operand shapes or dtypes")
     plan_arr = None
+    tensor_core = _band_candidate(q, path)      # a tensor-core kernel may run (the library decides)
     if path != PATH_GENERIC:
         if plan is None:
             plan = classify(sTod_lin, sTod_tr, nnzs)
         plan_arr = (ctypes.c_int32 * 8)(*plan)
+    if tensor_core:
+        _raise_if_gave_up(dev)
     sw = status_word(dev)
+    ran = ctypes.c_int32(0)
     with torch.cuda.device(dev):
-        check(_lib.splat_attention_fused(
+        check(_lib.splat_attention_fused_ex(
             q.data_ptr(), kt.data_ptr(), ksb, ksc, ksk, v.data_ptr(), output.data_ptr(),
             _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
             _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, float(scale), dtype_code(q.dtype),
             int(path), ctypes.cast(plan_arr, _vp) if plan_arr is not None else None,
-            sw.data_ptr(), _stream(dev)), "splat_attention_fused")
+            sw.data_ptr(), ctypes.byref(ran), _stream(dev)), "splat_attention_fused_ex")
+    if ran.value == PATH_BAND:
+        _refresh_mirror(dev)
+    elif q.dtype != torch.float32 and q.numel() > 0 and path == PATH_AUTO:
+        _warn_cuda_core_16bit("attention")
     if os.environ.get("SPLAT_B200_DEBUG"):
         check_status_word(dev)

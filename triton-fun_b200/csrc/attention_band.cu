@@ -998,6 +998,11 @@ static int32_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 
 }  // namespace band
 
+int32_t attention_pair(const void* q, const void* k, const void* v, void* o, const float* lin,
+                       const float* tr, const float* nnzs, int64_t bh, int64_t n_rows, int64_t stride,
+                       float scale, int32_t dtype, int32_t* status_word, int max_pairs,
+                       cudaStream_t st);
+
 int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                        const void* v, void* o, const float* lin, const float* tr,
                        const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
@@ -1020,13 +1025,25 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     if (plan[5] > n_cols || bh > 65535 || n_rows > INT32_MAX) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SPLAT_ERR_MISALIGNED;
 
-    // One Q tile per CTA (two CTAs per SM) when a class has a single row tile or the paired kernel
-    // would run fewer than ~16 waves (its per-CTA prologue and epilogue are not overlapped);
-    // SPLAT_B200_BAND_TILES=1|2 overrides.
+    // Kernel choice.  1: one Q tile per CTA (two CTAs per SM), for classes with a single row tile or
+    // problems too small to fill the GPU with larger units (per-CTA prologue and epilogue are not
+    // overlapped in the other kernels' first wave).  3: persistent CTA pairs (attention_pair.cu),
+    // d = 128 only.  2: two Q tiles per CTA, the remaining large problems (d = 64).
+    // SPLAT_B200_BAND_TILES=1|2|3 overrides; SPLAT_B200_PAIR_MAX limits the resident pairs of 3.
     const int64_t rows_v = n_rows / stride;
     const int64_t pair_items = ((rows_v + 2 * band::kTile - 1) / (2 * band::kTile)) * stride * bh;
-    bool single = rows_v <= band::kTile || pair_items < 16 * 148;
-    if (const char* e = getenv("SPLAT_B200_BAND_TILES")) single = e[0] == '1';
+    int variant = (rows_v <= band::kTile || pair_items < 16 * 148) ? 1 : 2;
+    if (const char* e = getenv("SPLAT_B200_BAND_TILES"))
+        if (e[0] >= '1' && e[0] <= '3') variant = e[0] - '0';
+    if (variant == 3 && d == 128) {
+        int max_pairs = 0;
+        if (const char* e = getenv("SPLAT_B200_PAIR_MAX")) max_pairs = atoi(e);
+        const int32_t rc = attention_pair(q, k, v, o, lin, tr, nnzs, bh, n_rows, stride, scale, dtype,
+                                          status_word, max_pairs, st);
+        if (rc != SPLAT_ERR_UNSUPPORTED_SHAPE) return rc;
+    }
+    if (variant == 3) variant = 2;
+    const bool single = variant == 1;
     const int kv_box = single ? band::kStep : band::kTile;
     CUtensorMap mq, mk, mv, mo;
     if (!band::make_map(&mq, q, dtype, bh, n_rows, d, stride) ||

@@ -63,12 +63,12 @@ extern "C" int32_t splat_attention_noalloc(const void* q, const void* k, int64_t
                                            const float* nnzs, int64_t bh, int64_t n_rows,
                                            int64_t n_cols, int64_t d, int64_t trailing_dim,
                                            float scale, int32_t dtype, void* stream) {
-    if (!q || !k || !v || !o || !sTod_lin || !sTod_tr || !nnzs || bh < 0 || n_rows < 0 ||
-        n_cols < 0 || d < 1 || trailing_dim < 0)
-        return SPLAT_ERR_BAD_ARG;
+    // sizes and dtype first; a problem without work is fine whatever its (possibly null) pointers
+    if (bh < 0 || n_rows < 0 || n_cols < 0 || d < 1 || trailing_dim < 0) return SPLAT_ERR_BAD_ARG;
     if (dtype != SPLAT_F32 && dtype != SPLAT_F16 && dtype != SPLAT_BF16)
         return SPLAT_ERR_UNSUPPORTED_DTYPE;
     if (bh == 0 || n_rows == 0) return SPLAT_OK;
+    if (!q || !k || !v || !o || !sTod_lin || !sTod_tr || !nnzs) return SPLAT_ERR_BAD_ARG;
     // overflow-safe size check against the fixed capacity
     const int64_t cap_elems = SPLAT_NOALLOC_SCRATCH_BYTES / splat::elem_size(dtype);
     if (trailing_dim > 0 && (bh > cap_elems / trailing_dim || bh * trailing_dim > cap_elems / n_rows))

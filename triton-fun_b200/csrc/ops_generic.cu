@@ -83,7 +83,7 @@ constexpr int kSoftmaxMaxVec = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-softmax_rows_vec_kernel(const T* __restrict__ s, T* __restrict__ p, const float* __restrict__ nnzs,
+softmax_rows_vec_kernel(const T* s, T* p, const float* __restrict__ nnzs,
                         int64_t total_rows, int64_t n_rows, int trailing, float scale_log2e) {
     constexpr int V = DT<T>::kVec;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -138,7 +138,7 @@ softmax_rows_vec_kernel(const T* __restrict__ s, T* __restrict__ p, const float*
 // keep HBM busy (one row per warp leaves the warp waiting on a single 512-byte request).
 template <typename T, int R>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-softmax_rows_short_kernel(const T* __restrict__ s, T* __restrict__ p, const float* __restrict__ nnzs,
+softmax_rows_short_kernel(const T* s, T* p, const float* __restrict__ nnzs,
                           int64_t total_rows, int64_t n_rows, int trailing, float scale_log2e) {
     constexpr int V = DT<T>::kVec;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -210,7 +210,7 @@ softmax_rows_short_kernel(const T* __restrict__ s, T* __restrict__ p, const floa
 
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-softmax_rows_loop_kernel(const T* __restrict__ s, T* __restrict__ p,
+softmax_rows_loop_kernel(const T* s, T* p,
                          const float* __restrict__ nnzs, int64_t total_rows, int64_t n_rows,
                          int trailing, float scale_log2e) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
