@@ -282,8 +282,12 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         // ------------------------------------------------------------------ MMA issuer of tile x
         // Uses ring item 2(n - n_lo) = K tile n and 2(n - n_lo) + 1 = V tile n; every item is
         // waited for and released exactly once by each issuer, used or not.
+        // The whole warp walks the loop on warp-uniform values and one elected lane issues: a
+        // single lane in a divergent branch needs about twice the tensor pipe's time per MMA just
+        // to get the instruction out.
         const int x = warp - kMmaWarp;
-        if (lane == 0 && any_work) {
+        if (any_work) {
+            const bool lead = elect_one();
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, 0);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
@@ -295,11 +299,15 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             bool ok = true;
 
             auto stage_of = [&](int item) { return item % kStages; };
-            auto full_wait = [&](int item) {
-                return mbar_wait(&ctrl->kv_full[stage_of(item)], (uint32_t)(item / kStages) & 1u,
-                                 status, kErrKvFull);
+            auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+                const bool r = mbar_wait(bar, parity, status, code);
+                return __all_sync(0xffffffffu, r) != 0;
             };
-            auto release = [&](int item) { mma_commit(&ctrl->kv_empty[stage_of(item)]); };
+            auto full_wait = [&](int item) {
+                return wait_all(&ctrl->kv_full[stage_of(item)], (uint32_t)(item / kStages) & 1u, kErrKvFull);
+            };
+            auto commit = [&](uint64_t* bar) { if (lead) mma_commit(bar); };
+            auto release = [&](int item) { commit(&ctrl->kv_empty[stage_of(item)]); };
             // S(k): 64 keys = rows [64(k&1), +64) of K tile k/2, into score buffer k&1
             auto issue_s = [&](int k) {
                 const uint32_t b_base = ring_addr + stage_of(2 * ((k >> 1) - n_lo)) * L::kTileBytes +
@@ -307,8 +315,9 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kSubBytes + (kk & 3) * 32;
-                    mma_ss(s_tmem + (k & 1) * kStep, smem_desc_sw128(q_base + off, 16, 1024),
-                           smem_desc_sw128(b_base + off, 16, 1024), idesc_qk, kk > 0);
+                    const uint64_t da = smem_desc_sw128(q_base + off, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(b_base + off, 16, 1024);
+                    if (lead) mma_ss(s_tmem + (k & 1) * kStep, da, db, idesc_qk, kk > 0);
                 }
             };
             // O += P(k) V(k): P packed in the first 32 columns of buffer k&1, V rows [64(k&1), +64)
@@ -316,15 +325,16 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 const uint32_t b_base = ring_addr + stage_of(2 * ((k >> 1) - n_lo) + 1) * L::kTileBytes +
                                         (k & 1) * (kStep * 128);
 #pragma unroll
-                for (int kk = 0; kk < kStep / 16; ++kk)
-                    mma_ts(o_tmem, s_tmem + (k & 1) * kStep + kk * 8,
-                           smem_desc_sw128(b_base + kk * 2048, kSubBytes, 1024), idesc_pv,
-                           (acc || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kStep / 16; ++kk) {
+                    const uint64_t db = smem_desc_sw128(b_base + kk * 2048, kSubBytes, 1024);
+                    if (lead) mma_ts(o_tmem, s_tmem + (k & 1) * kStep + kk * 8, db, idesc_pv,
+                                     (acc || kk > 0) ? 1u : 0u);
+                }
             };
             // last step of tile x that reads ring tile n
             auto last_user = [&](int k) { return (k & 1) == 1 || k == hi - 1; };
 
-            ok = mbar_wait(&ctrl->q_full, 0, status, kErrQ);
+            ok = wait_all(&ctrl->q_full, 0, kErrQ);
             if (hi > lo) {
                 const int t_lo = lo >> 1, t_hi = (hi + 1) >> 1;   // ring tiles tile x reads
                 // tiles before the range: pass them on untouched
@@ -340,7 +350,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_s(k);
-                    mma_commit(&ctrl->s_ready[x][k & 1]);
+                    commit(&ctrl->s_ready[x][k & 1]);
                     if (last_user(k)) release(item_k);
                 }
                 uint32_t p_phase[2] = {0, 0};
@@ -349,7 +359,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (k == lo || (k & 1) == 0) ok = full_wait(item_v);
                     if (!ok) break;
                     SPLAT_TRACE(2 + x, 10);
-                    ok = mbar_wait(&ctrl->p_ready[x][k & 1], p_phase[k & 1], status, kErrPReady);
+                    ok = wait_all(&ctrl->p_ready[x][k & 1], p_phase[k & 1], kErrPReady);
                     if (!ok) break;
                     p_phase[k & 1] ^= 1u;
                     tc_fence_after_sync();
@@ -365,7 +375,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         if (last_user(k + 2)) release(item_k);
                     }
                     // buffer k&1: next scores ready -- and, in any case, PV(k) complete
-                    mma_commit(&ctrl->s_ready[x][k & 1]);
+                    commit(&ctrl->s_ready[x][k & 1]);
                     SPLAT_TRACE(2 + x, 12);
                 }
                 // tiles after the range
@@ -382,9 +392,10 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
             if (!ok) {
                 // let the tensor pipe drain before tensor memory is released
-                mma_commit(&ctrl->drain[x]);
+                commit(&ctrl->drain[x]);
                 mbar_wait_quiet(&ctrl->drain[x], 0);
             }
+            __syncwarp();
         }
     } else if (warp < 8) {
         // ------------------------------------------------------------------ softmax + epilogue
@@ -700,67 +711,75 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // ------------------------------------------------------------------ MMA issuer
         // ring item 2(k - klo) = K(k), 2(k - klo) + 1 = V(k); order S(klo), S(klo+1), then per k:
         // PV(k), S(k+2)
-        if (lane == 0 && steps > 0) {
+        // (whole warp on warp-uniform values, one elected lane issues: see the paired kernel)
+        if (steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, 0);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
+            const bool lead = elect_one();
             const uint32_t ring_addr = smem_u32(s_ring), q_base = smem_u32(s_q);
             const uint32_t o_tmem = tmem_base + 2 * kStep;
+            auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+                const bool r = mbar_wait(bar, parity, status, code);
+                return __all_sync(0xffffffffu, r) != 0;
+            };
+            auto commit = [&](uint64_t* bar) { if (lead) mma_commit(bar); };
             auto full_wait = [&](int item) {
-                return mbar_wait(&ctrl->kv_full[item % kStages], (uint32_t)(item / kStages) & 1u,
-                                 status, kErrKvFull);
+                return wait_all(&ctrl->kv_full[item % kStages], (uint32_t)(item / kStages) & 1u, kErrKvFull);
             };
             auto issue_s = [&](int k) {
                 const uint32_t b_base = ring_addr + ((2 * (k - klo)) % kStages) * L::kItemBytes;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    mma_ss(tmem_base + (k & 1) * kStep,
-                           smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024),
-                           smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024),
-                           idesc_qk, kk > 0);
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t da = smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024);
+                    if (lead) mma_ss(tmem_base + (k & 1) * kStep, da, db, idesc_qk, kk > 0);
+                }
             };
             auto issue_pv = [&](int k, bool acc) {
                 const uint32_t b_base = ring_addr + ((2 * (k - klo) + 1) % kStages) * L::kItemBytes;
 #pragma unroll
-                for (int kk = 0; kk < kStep / 16; ++kk)
-                    mma_ts(o_tmem, tmem_base + (k & 1) * kStep + kk * 8,
-                           smem_desc_sw128(b_base + kk * 2048, kStepBytesPerSub, 1024), idesc_pv,
-                           (acc || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kStep / 16; ++kk) {
+                    const uint64_t db = smem_desc_sw128(b_base + kk * 2048, kStepBytesPerSub, 1024);
+                    if (lead) mma_ts(o_tmem, tmem_base + (k & 1) * kStep + kk * 8, db, idesc_pv,
+                                     (acc || kk > 0) ? 1u : 0u);
+                }
             };
-            bool ok = mbar_wait(&ctrl->q_full, 0, status, kErrQ);
+            bool ok = wait_all(&ctrl->q_full, 0, kErrQ);
             for (int k = klo; k < min(klo + 2, khi) && ok; ++k) {
                 ok = full_wait(2 * (k - klo));
                 if (!ok) break;
                 tc_fence_after_sync();
                 issue_s(k);
-                mma_commit(&ctrl->s_ready[k & 1]);
-                mma_commit(&ctrl->kv_empty[(2 * (k - klo)) % kStages]);
+                commit(&ctrl->s_ready[k & 1]);
+                commit(&ctrl->kv_empty[(2 * (k - klo)) % kStages]);
             }
             uint32_t p_phase[2] = {0, 0};
             for (int k = klo; k < khi && ok; ++k) {
                 const int item_v = 2 * (k - klo) + 1;
                 ok = full_wait(item_v);
                 if (!ok) break;
-                ok = mbar_wait(&ctrl->p_ready[k & 1], p_phase[k & 1], status, kErrPReady);
+                ok = wait_all(&ctrl->p_ready[k & 1], p_phase[k & 1], kErrPReady);
                 if (!ok) break;
                 p_phase[k & 1] ^= 1u;
                 tc_fence_after_sync();
                 issue_pv(k, k > klo);
-                mma_commit(&ctrl->kv_empty[item_v % kStages]);
+                commit(&ctrl->kv_empty[item_v % kStages]);
                 if (k + 2 < khi) {
                     const int item_k = 2 * (k + 2 - klo);
                     ok = full_wait(item_k);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_s(k + 2);
-                    mma_commit(&ctrl->kv_empty[item_k % kStages]);
+                    commit(&ctrl->kv_empty[item_k % kStages]);
                 }
-                mma_commit(&ctrl->s_ready[k & 1]);   // next scores ready, and PV(k) complete
+                commit(&ctrl->s_ready[k & 1]);   // next scores ready, and PV(k) complete
             }
             if (!ok) {
-                mma_commit(&ctrl->drain);
+                commit(&ctrl->drain);
                 mbar_wait_quiet(&ctrl->drain, 0);
             }
+            __syncwarp();
         }
     } else if (warp < 4) {
         // ------------------------------------------------------------------ softmax + epilogue
