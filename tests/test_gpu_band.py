@@ -1,4 +1,4 @@
-"""GPU: the TMA + tcgen05 band kernel against the CPU oracle, over window / blocked / strided / dilated patterns, ragged sizes and both 16-bit dtypes."""
+"""GPU: the TMA + tcgen05 band kernels (one Q tile per CTA, two Q tiles per CTA, CTA pairs) against the CPU oracle, over window / blocked / strided / dilated patterns, ragged sizes and both 16-bit dtypes."""
 import pytest
 import torch
 
@@ -23,10 +23,11 @@ PATTERNS = [
 ]
 
 
-@pytest.fixture(params=["1", "2"], ids=["one-tile-ctas", "paired-tile-ctas"], autouse=True)
+@pytest.fixture(params=["1", "2", "3"], ids=["one-tile-ctas", "paired-tile-ctas", "cta-pairs"], autouse=True)
 def band_variant(request, monkeypatch):
-    """Every test runs against both band kernels: one Q tile per CTA (two CTAs per SM) and two Q
-    tiles per CTA.  The library reads the override at each call."""
+    """Every test runs against the three band kernels: one Q tile per CTA (two CTAs per SM), two Q
+    tiles per CTA, and persistent CTA pairs (cta_group::2; d = 128 only, d = 64 falls back to the
+    two-tile kernel).  The library reads the override at each call."""
     monkeypatch.setenv("SPLAT_B200_BAND_TILES", request.param)
     return request.param
 
@@ -103,6 +104,52 @@ def test_band_path_refuses_what_it_cannot_do():
         n.attention_fused(q32, q32.transpose(2, 3), q32, torch.empty_like(q32), acsr[2], acsr[3],
                           acsr[4], 1.0, n.PATH_BAND)
     torch.cuda.synchronize()
+
+
+def test_auto_path_takes_operands_the_band_path_cannot():
+    """Operands that are not 16-byte aligned: the tensor-core path refuses them when asked for
+    explicitly and SPLAT_PATH_AUTO computes the result with the general kernel."""
+    import acsr_helpers as ah
+    import splat_native as n
+    L, d = 256, 128
+    acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 63), 16, 0)
+    meta = ao.metadata_from_pattern(ao.PATTERN_CAUSAL_WINDOWED, L, 63, 0, 16)
+    torch.manual_seed(3)
+    pool = torch.randn(3, L * d + 8, device="cuda").to(torch.bfloat16)
+    # views that start one element (2 bytes) into their allocation
+    q, k, v = (pool[i, 1:1 + L * d].view(1, 1, L, d) for i in range(3))
+    o = torch.empty(L * d + 8, dtype=torch.bfloat16, device="cuda")[1:1 + L * d].view(1, 1, L, d)
+    assert q.data_ptr() % 16 != 0
+    with pytest.raises(RuntimeError):
+        n.attention_fused(q, k.transpose(2, 3), v, o, acsr[2], acsr[3], acsr[4], d ** -0.5, n.PATH_BAND)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        n.attention_fused(q, k.transpose(2, 3), v, o, acsr[2], acsr[3], acsr[4], d ** -0.5, n.PATH_AUTO)
+    ref = at.attention_acsr(q.cpu(), k.cpu().transpose(2, 3), v.cpu(), meta, meta["trailing_dim"], d ** -0.5)
+    assert_close(o, ref, torch.bfloat16, "unaligned operands through AUTO")
+
+
+def test_launcher_reports_an_earlier_timeout():
+    """The Python launchers keep a pinned mirror of the status word: a launch made after a kernel
+    gave up raises instead of returning an untouched output buffer."""
+    import acsr_helpers as ah
+    import splat_native as n
+    L, d = 256, 128
+    acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 63), 16, 0)
+    q = torch.randn(1, 1, L, d, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    dev = torch.device("cuda", 0)
+    n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+    torch.cuda.synchronize()
+    n.status_word(dev).fill_(5)            # as if a wait had run out inside that kernel
+    n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)  # no-op on the device
+    torch.cuda.synchronize()               # lets the mirror copy land
+    with pytest.raises(RuntimeError):
+        n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+    # the raise cleared the word: back to normal
+    n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+    n.check_status_word(0)
 
 
 def test_bounded_wait_gives_up_and_reports(band_variant):

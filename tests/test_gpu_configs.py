@@ -51,19 +51,28 @@ def test_config1_full():
 
 
 @pytest.mark.parametrize("cfg", [2, 3, 4, 5])
-def test_config_sampled_heads_against_oracle(cfg):
-    """Full sequence length and pattern, two heads, every row compared with the CPU oracle."""
+def test_config_sampled_heads_against_oracle(cfg, monkeypatch):
+    """Full sequence length and pattern, two heads, every row compared with the CPU oracle -- for
+    the kernel the library picks at this size and for each of the three band kernels forced
+    (1: one Q tile per CTA, 2: two Q tiles per CTA, the kernel the full-size benchmark of
+    configuration 5 runs, 3: CTA pairs)."""
     import splat_native as n
     B, H, L, d, dtype, kind, p0, p1, spread, seed = CONFIGS[cfg]
     heads = 2
     q, k, v = _inputs(cfg, heads)
     meta = ao.metadata_from_pattern(kind, L, p0, p1, 16)
-    attn = _module(cfg, heads, path=n.PATH_BAND)
-    out = attn([q, k.transpose(2, 3), v])
-    attn.check_status()
     ref = at.attention_acsr(q.cpu(), k.cpu().transpose(2, 3), v.cpu(), meta, meta["trailing_dim"],
                             d ** -0.5)
-    assert_close(out, ref, dtype, f"config {cfg} band")
+    for variant in (None, "1", "2", "3"):
+        if variant is None:
+            monkeypatch.delenv("SPLAT_B200_BAND_TILES", raising=False)
+        else:
+            monkeypatch.setenv("SPLAT_B200_BAND_TILES", variant)
+        attn = _module(cfg, heads, path=n.PATH_BAND)
+        out = attn([q, k.transpose(2, 3), v])
+        attn.check_status()
+        assert_close(out, ref, dtype, f"config {cfg} band kernel {variant or 'auto'}")
+    monkeypatch.delenv("SPLAT_B200_BAND_TILES", raising=False)
     # the three-launch path of the reference API on the same inputs (one head: S and P are large)
     attn3 = _module(cfg, 1, fused=False)
     out3 = attn3([q[:, :1].contiguous(), k[:, :1].contiguous().transpose(2, 3), v[:, :1].contiguous()])

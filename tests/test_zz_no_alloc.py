@@ -46,16 +46,25 @@ def _noalloc(n, q, kt, v, acsr, scale):
 
 
 def test_noalloc_matches_existing_entry_points_twice_in_a_row():
+    """Calls in a row of different shape and dtype: each finds the previous call's leftovers in the
+    shared array.  The trailing dimensions are chosen so that the in-place softmax runs through
+    each of its three kernels (201 and 17: the general loop; 256: short rows, two per warp; 512:
+    rows held in registers).  Every result must equal the three existing entry points' bit for bit
+    and agree with the CPU oracle within the library's tolerances."""
     import acsr_helpers as ah
     import splat_native as n
+    from conftest import assert_close
+    from oracle import attention_oracle as at
     torch.manual_seed(21)
-    calls = [  # (pattern, dtype, B, H, d): the second problem is smaller and of another dtype
-        (ah.create_causal_windowed_mask(640, 200), torch.bfloat16, 2, 3, 64),
-        (ah.create_dilated_mask(300, 17, 3), torch.float32, 1, 2, 32),
+    calls = [  # (pattern kind, L, p0, p1, dtype, B, H, d)
+        (ao.PATTERN_CAUSAL_WINDOWED, 640, 200, 0, torch.bfloat16, 2, 3, 64),
+        (ao.PATTERN_DILATED, 300, 17, 3, torch.float32, 1, 2, 32),
+        (ao.PATTERN_CAUSAL_WINDOWED, 1024, 255, 0, torch.bfloat16, 1, 2, 64),
+        (ao.PATTERN_CAUSAL_WINDOWED, 1024, 511, 0, torch.float16, 1, 2, 32),
     ]
-    for mask, dtype, B, H, d in calls:
-        L = len(mask)
-        acsr = ah.create_acsr(mask, 16, 0)
+    for kind, L, p0, p1, dtype, B, H, d in calls:
+        acsr = ah.create_acsr(ah.PatternMask(kind, L, p0, p1), 16, 0)
+        meta = ao.metadata_from_pattern(kind, L, p0, p1, 16)
         q, k, v = (torch.randn(B, H, L, d, device="cuda").to(dtype) for _ in range(3))
         kt = k.transpose(2, 3)
         scale = d ** -0.5
@@ -64,6 +73,20 @@ def test_noalloc_matches_existing_entry_points_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
         assert torch.equal(got, expect), f"max diff {(got.float() - expect.float()).abs().max().item()}"
+        ref = at.attention_acsr(q.cpu(), kt.cpu(), v.cpu(), meta, meta["trailing_dim"], scale)
+        assert_close(got, ref, dtype, f"no-alloc vs oracle, trailing_dim {acsr[5]}")
+
+
+def test_noalloc_empty_problem_needs_no_buffers():
+    """No (batch, head) pairs or no rows: nothing to do, null data pointers are fine."""
+    import splat_native as n
+    stream = torch.cuda.current_stream().cuda_stream
+    for bh, rows in ((0, 128), (3, 0)):
+        rc = n._lib.splat_attention_noalloc(None, None, 0, 64, 1, None, None, None, None, None, bh, rows,
+                                            rows, 64, 16, ctypes.c_float(1.0),
+                                            n.dtype_code(torch.bfloat16), stream)
+        assert rc == 0, n.status_string(rc)
+    torch.cuda.synchronize()
 
 
 def test_noalloc_refuses_problems_beyond_its_fixed_buffer():

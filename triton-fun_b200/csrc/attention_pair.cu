@@ -13,32 +13,37 @@
 // (both CTAs together, every MMA has M = 256: 128 rows per SM):
 //     S(G) = Q K^T        8 x tcgen05.mma 256x128x16, A = each CTA's Q tile, B = the key tile: each
 //                         CTA holds 64 of the 128 keys in its own shared memory
-//     P(G) = exp2(S c - m) softmax warps of each CTA on their own 128 rows (thread = row): scores
-//                         from tensor memory, band mask, running max with lazy rescale of O,
-//                         16-bit P stored over the consumed scores
-//     O  += P(G) V        8 x tcgen05.mma 256x128x16, A = P from each CTA's tensor memory,
-//                         B = the value tile: each CTA holds 64 of the 128 value columns
-// Each SM's 512 tensor-memory columns hold THREE score buffers (step G uses buffer G mod 3) and O,
-// so the tensor core runs up to three steps ahead of the softmax warps, also into the next item:
-// issue order S(0) S(1) S(2), then per step PV(G), S(G+3).  Operand halves are loaded by each CTA
-// for itself with plain TMA loads (no multicast); the byte counts of both CTAs land on barriers of
-// the even CTA, whose MMA warp is the only consumer.
+//     P(G) = exp2(S c - m) softmax warps on their CTA's 128 rows, TWO threads per row: one for the
+//                         step's keys 0..63, one for keys 64..127.  Each keeps its own running
+//                         maximum and sum (lazy rescale) and stores its 16-bit P over the scores
+//                         it consumed
+//     O_h += P_h(G) V_h   per key half h: 4 x tcgen05.mma 256x128x16, A = P from each CTA's tensor
+//                         memory, B = the value tile (each CTA holds 64 of the 128 value columns)
+// The two key halves are two independent online-softmax streams with their own accumulators O_0,
+// O_1; the epilogue merges them: O = (a_0 O_0 + a_1 O_1) / (a_0 l_0 + a_1 l_1), a_h = 2^(m_h - m).
+// That puts two softmax warps on every scheduler (one's exponentials cover the other's loads,
+// maxima and handshakes) without any exchange between the two threads of a row.  Each SM's 512
+// tensor-memory columns hold two score buffers (step G uses buffer G mod 2), O_0 and O_1; the
+// tensor core runs up to two steps ahead of the softmax warps, also into the next item: issue
+// order S(0) S(1), then per step PV(G), S(G+2).  Operand halves are loaded by each CTA for itself
+// with plain TMA loads (no multicast); the byte counts of both CTAs land on barriers of the even
+// CTA, whose MMA warp is the only consumer.
 //
 // Progress of the tensor core is published as numbered EVENTS: event e is one tcgen05.commit per
-// CTA onto barrier e mod 32 of that CTA.  Event G = "S(G) complete", event G + 3 = "PV(G)
-// complete" (one commit after PV(G), S(G+3) serves both).  Softmax warps wait for S(G); epilogue
+// CTA onto barrier e mod 32 of that CTA.  Event G = "S(G) complete", event G + 2 = "PV(G)
+// complete" (one commit after PV(G), S(G+2) serves both).  Softmax warps wait for S(G); epilogue
 // warps for the PV of their rows' last step; the TMA producers for the event that frees the slot
 // they are about to overwrite.  Every role walks the same item list with the per-item (n_lo, N)
 // taken from a table in shared memory that each CTA builds from the row metadata at kernel start,
 // so no role has to tell another what comes next.
 //
-// Warps per CTA (three warpgroups with their own register budgets): 0-3 softmax (never wait for a
-// PV except to rescale O), 4-7 epilogue (normalise O
-// with the row sums the softmax warps leave in shared memory, stage, TMA store; this overlaps the
-// next item's softmax), 8 TMA producer, 9 MMA issuer (even CTA; the whole warp runs the loop and
-// one elected lane issues) and tensor-memory owner (both).  Every mbarrier wait is bounded; a role
-// that gives up records a code in the status word, the others see the word in their own waits,
-// and both CTAs meet at a cluster barrier before tensor memory is released and either CTA leaves.
+// Warps per CTA: 0-3 softmax of keys 0..63, 4-7 softmax of keys 64..127 (never wait for a PV
+// except to rescale their O), 8-11 epilogue (merge and normalise O with the maxima and sums the
+// softmax warps leave in shared memory, stage, TMA store; this overlaps the next item's softmax),
+// 12 TMA producer, 13 MMA issuer (even CTA; the whole warp runs the loop and one elected lane
+// issues) and tensor-memory owner (both), 14-15 idle.  Every mbarrier wait is bounded; a role that
+// gives up records a code in the status word, the others see the word in their own waits, and
+// both CTAs meet at a cluster barrier before tensor memory is released and either CTA leaves.
 #include <limits.h>
 #include <mutex>
 #include <type_traits>
@@ -62,26 +67,22 @@ constexpr int D = 128;
 constexpr int kTile = 128;             // rows per CTA and keys per step
 constexpr int kHalf = 64;              // score columns a softmax thread holds at a time
 constexpr int kItemRows = 2 * kTile;   // rows per work item (CTA pair)
-constexpr int kThreads = 384;           // 12 warps: softmax 0-3, epilogue 4-7, TMA 8, MMA 9, two idle
+constexpr int kThreads = 512;          // 16 warps: softmax 0-7, epilogue 8-11, TMA 12, MMA 13, two idle
 constexpr int kWarps = kThreads / 32;
-constexpr int kEpiWarp = 4;            // warps 4..7
-constexpr int kTmaWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kEpiWarp = 8;            // warps 8..11
+constexpr int kTmaWarp = 12;
+constexpr int kMmaWarp = 13;
 constexpr int kTmemCols = 512;
-constexpr int kBufs = 3;               // score buffers = K slots = V slots
+constexpr int kBufs = 2;               // score buffers
+constexpr int kSlots = 3;              // K slots = V slots (Cursor::slot counts modulo 3)
 constexpr int kEvents = 32;            // event barriers: a wait must be issued before its event is 32 events old
 constexpr int kMaxEntries = 2048;      // (residue class, row block) combinations the range table holds
 constexpr int kSubBytes = kTile * 128;         // 128 rows of one 64-element column chunk
 constexpr int kTileBytes = 2 * kSubBytes;      // Q tile / O staging: 128 rows x 128 columns
 constexpr int kSlotBytes = 16384;              // K half (64 keys x 128) or V half (128 keys x 64)
 constexpr int kKHalfSub = 64 * 128;            // one 64-element chunk of a K half
-constexpr uint32_t kOCol = 3 * kTile;          // tensor-memory column of O
+constexpr uint32_t kOCol = 2 * kTile;          // tensor-memory column of O_0; O_1 follows
 constexpr float kRescaleThreshold = 8.0f;
-constexpr int kRegsSoftmax = 232, kRegsEpilogue = 152, kRegsOther = 96;   // 128 * sum <= 64 K registers
-#ifndef SPLAT_PAIR_POLY_PAIRS
-#define SPLAT_PAIR_POLY_PAIRS 0
-#endif
-constexpr int kPolyPairs = SPLAT_PAIR_POLY_PAIRS;   // of every 4 pairs of exponentials, on the FMA pipes
 
 // status-word codes (which wait gave up)
 enum : int { kErrQ = 11, kErrKFull = 12, kErrVFull = 13, kErrEvent = 14, kErrPReady = 15,
@@ -106,18 +107,18 @@ struct Params {
 struct Control {
     uint64_t ev[kEvents];      // both CTAs: tensor-core progress events
     uint64_t q_full[2];        // even CTA only (as the next four): Q tiles of both CTAs have landed
-    uint64_t k_full[kBufs];
-    uint64_t v_full[kBufs];
-    uint64_t p_ready[kBufs];   // 8 arrivals: the softmax warps of both CTAs
+    uint64_t k_full[kSlots];
+    uint64_t v_full[kSlots];
+    uint64_t p_ready[kBufs];   // 16 arrivals: the softmax warps of both CTAs
     uint64_t o_free;           // 8 arrivals: O has been read out, the next item may overwrite it
     uint64_t drain;
-    uint64_t l_full[2];        // own CTA, 4 arrivals: row sums of an item are in l_buf (items alternate)
+    uint64_t l_full[2];        // own CTA, 8 arrivals: maxima and sums of an item are in ml_buf (items alternate)
     uint64_t l_free[2];        // own CTA, 4 arrivals: the epilogue warps have read them
     uint64_t stage_free;       // own CTA: the previous TMA store has read the output staging buffer
     uint64_t stage_ready;      // own CTA, 4 arrivals: the epilogue warps have written their rows
     uint32_t tmem_base;
     int32_t abort_at_entry;
-    float l_buf[2][kTile];
+    float2 ml_buf[2][2][kTile];    // [item parity][key half][row] = (running maximum, sum)
     uint32_t range[kMaxEntries];   // per (class, row block): n_lo | N << 16
 };
 
@@ -125,15 +126,15 @@ struct Layout {
     static constexpr int kQOff = 0;                               // two Q tiles (items alternate)
     static constexpr int kStageOff = 2 * kTileBytes;              // output staging
     static constexpr int kKOff = kStageOff + kTileBytes;
-    static constexpr int kVOff = kKOff + kBufs * kSlotBytes;
-    static constexpr int kCtrlOff = kVOff + kBufs * kSlotBytes;
+    static constexpr int kVOff = kKOff + kSlots * kSlotBytes;
+    static constexpr int kCtrlOff = kVOff + kSlots * kSlotBytes;
     static constexpr int kSmemBytes = kCtrlOff + (int)sizeof(Control) + 1024;   // + alignment slack
 };
 
 #ifdef SPLAT_PAIR_TRACE
 #define PAIR_TRACE(role, tag)                                                                     \
     do {                                                                                          \
-        if (trace_on && lane == 0 && (warp & 3) == (warp < 8 ? 0 : warp & 3) && trace_n < 2048)    \
+        if (trace_on && lane == 0 && (warp == 0 || warp == 8 || warp >= 12) && trace_n < 2048) \
             p.trace[(role) * 2048 + trace_n++] = ((long long)(tag) << 48) | (clock64() & 0xffffffffffffLL); \
     } while (0)
 #else
@@ -163,8 +164,56 @@ struct Cursor {
     int64_t G;        // global step
     int i, N, n_lo;   // step within the item, steps of the item, first key tile of the item
     int jq;           // items with steps before this one
+    int slot;         // G mod kSlots
     int block, res;
     bool valid;
+};
+
+// The item list of one CTA pair and its step ranges.  Built inside each role (from special
+// registers, so the compiler keeps it there) rather than once per thread: values shared by all
+// roles would have to live in registers across the roles' different register budgets.
+struct Walk {
+    int64_t first, step, step_bh, n_items;
+    int step_e, n_entries, items_per_class;
+    const uint32_t* range;
+
+    __device__ __forceinline__ void begin(ItemPos& at) const {
+        at.w = first;
+        at.e = (int)(first % n_entries);
+        at.bh = first / n_entries;
+    }
+    // w -> w + step without 64-bit divisions
+    __device__ __forceinline__ void next(ItemPos& at) const {
+        at.w += step;
+        at.e += step_e;
+        at.bh += step_bh;
+        if (at.e >= n_entries) { at.e -= n_entries; ++at.bh; }
+    }
+    // item at c.at -> class, block and range; false when the item has no steps
+    __device__ __forceinline__ bool load(Cursor& c) const {
+        c.res = c.at.e / items_per_class;
+        c.block = c.at.e - c.res * items_per_class;
+        const uint32_t r = range[c.at.e];
+        c.n_lo = (int)(r & 0xffffu);
+        c.N = (int)(r >> 16);
+        return c.N > 0;
+    }
+    __device__ __forceinline__ void cursor_begin(Cursor& c) const {
+        begin(c.at);
+        c.G = 0; c.i = 0; c.jq = 0; c.slot = 0;
+        c.valid = false;
+        for (; c.at.w < n_items; next(c.at))
+            if (load(c)) { c.valid = true; break; }
+    }
+    __device__ __forceinline__ void cursor_next(Cursor& c) const {
+        ++c.G;
+        c.slot = c.slot == 2 ? 0 : c.slot + 1;
+        if (++c.i < c.N) return;
+        c.i = 0; ++c.jq;
+        c.valid = false;
+        for (next(c.at); c.at.w < n_items; next(c.at))
+            if (load(c)) { c.valid = true; break; }
+    }
 };
 
 __device__ __forceinline__ void spin_cycles(long long n) {
@@ -172,34 +221,18 @@ __device__ __forceinline__ void spin_cycles(long long n) {
     while (clock64() - t0 < n) { }
 }
 
-// Keeps the compiler from using registers a tcgen05.ld writes before the wait that follows it.
-__device__ __forceinline__ void reg_fence16(uint32_t* r) {
-    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
-                      "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
-                      "+r"(r[13]), "+r"(r[14]), "+r"(r[15]));
-}
-__device__ __forceinline__ void reg_fence64(uint32_t* r) {
-    reg_fence16(r); reg_fence16(r + 16); reg_fence16(r + 32); reg_fence16(r + 48);
-}
-
-// x[J0..J1) of a 64-score half -> packed 16-bit probabilities exp2(s*c - m) in x[J0/2..J1/2); row
-// sums into acc0/acc1.  kPolyPairs of every four pairs are evaluated on the FMA pipes, the rest on
-// the special function unit (16 exp2 per clock and SM: the narrowest pipe of the softmax).
-template <typename T, int J0, int J1>
-__device__ __forceinline__ void exp_part(uint32_t* x, float2 sc2, float2 nm2, float2& acc0, float2& acc1) {
+// x[0..64) scores -> packed 16-bit probabilities exp2(s*c - m) in x[0..32); row sums into acc0/acc1.
+template <typename T>
+__device__ __forceinline__ void exp_half(uint32_t* x, float2 sc2, float2 nm2, float2& acc0, float2& acc1) {
 #pragma unroll
-    for (int j = J0; j < J1; j += 8) {
+    for (int j = 0; j < kHalf; j += 8) {
         float2 a[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-            a[c] = fma2(make_float2(__uint_as_float(x[j + 2 * c]), __uint_as_float(x[j + 2 * c + 1])), sc2, nm2);
-#ifndef SPLAT_ABL_NOEXP
-#pragma unroll
         for (int c = 0; c < 4; ++c) {
-            if (c < kPolyPairs) a[c] = ex2_poly2(a[c]);
-            else { a[c].x = ex2(a[c].x); a[c].y = ex2(a[c].y); }
+            a[c] = fma2(make_float2(__uint_as_float(x[j + 2 * c]), __uint_as_float(x[j + 2 * c + 1])), sc2, nm2);
+            a[c].x = ex2(a[c].x);
+            a[c].y = ex2(a[c].y);
         }
-#endif
         acc0 = add2(acc0, add2(a[0], a[1]));
         acc1 = add2(acc1, add2(a[2], a[3]));
 #pragma unroll
@@ -207,38 +240,39 @@ __device__ __forceinline__ void exp_part(uint32_t* x, float2 sc2, float2 nm2, fl
     }
 }
 
-// Band edge: columns of half H outside [v_lo, v_hi) (step-relative) become -inf; then the row maximum.
-template <int H>
-__device__ __forceinline__ float masked_max(uint32_t* x, int v_lo, int v_hi, bool lo_ok, bool hi_ok) {
-    if (!lo_ok && !hi_ok) {
+// Band edge: columns outside [v_lo, v_lo + width) (relative to x[0]) become -inf; then the row
+// maximum.  One unsigned comparison per column covers both ends.
+__device__ __forceinline__ float masked_max(uint32_t* x, int v_lo, int width, bool edge) {
+    if (edge) {
 #pragma unroll
         for (int j = 0; j < kHalf; ++j)
-            x[j] = (j + H * kHalf >= v_lo && j + H * kHalf < v_hi) ? x[j] : 0xff800000u;
-    } else if (!hi_ok) {
-#pragma unroll
-        for (int j = 0; j < kHalf; ++j) x[j] = j + H * kHalf < v_hi ? x[j] : 0xff800000u;
-    } else if (!lo_ok) {
-#pragma unroll
-        for (int j = 0; j < kHalf; ++j) x[j] = j + H * kHalf >= v_lo ? x[j] : 0xff800000u;
+            x[j] = (uint32_t)(j - v_lo) < (uint32_t)width ? x[j] : 0xff800000u;
     }
-    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    float mx[8];
 #pragma unroll
-    for (int j = 0; j < kHalf; j += 8) {
+    for (int c = 0; c < 8; ++c) mx[c] = fmaxf(__uint_as_float(x[2 * c]), __uint_as_float(x[2 * c + 1]));
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+    for (int j = 16; j < kHalf; j += 16) {      // eight independent chains of 3-input max
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
             mx[c] = fmax3(mx[c], __uint_as_float(x[j + 2 * c]), __uint_as_float(x[j + 2 * c + 1]));
     }
-    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    return fmaxf(fmax3(mx[0], mx[1], mx[2]), fmax3(fmax3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
 }
 
-template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t w);
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
-    return __half22float2(*reinterpret_cast<__half2*>(&w));
+// Rare paths of the lazy rescale, kept out of line so that the softmax loop stays small.
+// O rows of this thread (128 fp32 columns at o_addr) *= corr.
+__device__ __noinline__ void rescale_o(uint32_t o_addr, float corr) {
+#pragma unroll 1
+    for (int ch = 0; ch < D / 16; ++ch) {
+        uint32_t o[16];
+        tmem_ld16(o_addr + ch * 16, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+        tmem_st16(o_addr + ch * 16, o);
+    }
 }
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
-    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -256,11 +290,8 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     volatile int32_t* status = p.status;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();            // 0 = even CTA (issues the MMAs)
-    const int64_t first_item = cluster_id_x();
-    const int64_t item_step = cluster_count_x();
 #ifdef SPLAT_PAIR_TRACE
-    const bool trace_on = p.trace != nullptr && first_item == item_step / 2 && rank == 0;
+    const bool trace_on = p.trace != nullptr && cluster_id_x() == cluster_count_x() / 2 && cluster_ctarank() == 0;
     int trace_n = 0;
 #endif
 
@@ -273,14 +304,14 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int i = 0; i < kEvents; ++i) mbar_init(&ctrl->ev[i], 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctrl->q_full[i], 1);
-            mbar_init(&ctrl->l_full[i], 4);
+            mbar_init(&ctrl->l_full[i], 8);
             mbar_init(&ctrl->l_free[i], 4);
         }
-        for (int i = 0; i < kBufs; ++i) {
+        for (int i = 0; i < kSlots; ++i) {
             mbar_init(&ctrl->k_full[i], 1);
             mbar_init(&ctrl->v_full[i], 1);
-            mbar_init(&ctrl->p_ready[i], 8);
         }
+        for (int i = 0; i < kBufs; ++i) mbar_init(&ctrl->p_ready[i], 16);
         mbar_init(&ctrl->o_free, 8);
         mbar_init(&ctrl->drain, 1);
         mbar_init(&ctrl->stage_free, 1);
@@ -313,7 +344,6 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     __syncthreads();
     cluster_sync_all();      // the other CTA's barriers are initialised before anything targets them
     tc_fence_after_sync();
-    const uint32_t tmem_base = ctrl->tmem_base;
     // both CTAs read the same global word; a differing view could only come from a concurrent
     // writer, i.e. a kernel that is giving up right now, and then the bounded waits end this one too
     const bool run = ctrl->abort_at_entry == 0;
@@ -323,56 +353,28 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     auto event_wait = [&](int64_t e, int code) {
         return mbar_wait(&ctrl->ev[e & (kEvents - 1)], (uint32_t)(e >> 5) & 1u, status, code);
     };
-    // walking the item list: w -> w + item_step without 64-bit divisions
-    const int step_e = (int)(item_step % p.n_entries);
-    const int64_t step_bh = item_step / p.n_entries;
-    auto pos_begin = [&](ItemPos& at) {
-        at.w = first_item;
-        at.e = (int)(first_item % p.n_entries);
-        at.bh = first_item / p.n_entries;
-    };
-    auto pos_next = [&](ItemPos& at) {
-        at.w += item_step;
-        at.e += step_e;
-        at.bh += step_bh;
-        if (at.e >= p.n_entries) { at.e -= p.n_entries; ++at.bh; }
-    };
-    // item at c.at -> class, block and range; false when the item has no steps
-    auto load_item = [&](Cursor& c) {
-        c.res = c.at.e / p.items_per_class;
-        c.block = c.at.e - c.res * p.items_per_class;
-        const uint32_t r = ctrl->range[c.at.e];
-        c.n_lo = (int)(r & 0xffffu);
-        c.N = (int)(r >> 16);
-        return c.N > 0;
-    };
-    auto cursor_begin = [&](Cursor& c) {
-        pos_begin(c.at);
-        c.G = 0; c.i = 0; c.jq = 0;
-        c.valid = false;
-        for (; c.at.w < p.n_items; pos_next(c.at))
-            if (load_item(c)) { c.valid = true; break; }
-    };
-    auto cursor_next = [&](Cursor& c) {
-        ++c.G;
-        if (++c.i < c.N) return;
-        c.i = 0; ++c.jq;
-        c.valid = false;
-        for (pos_next(c.at); c.at.w < p.n_items; pos_next(c.at))
-            if (load_item(c)) { c.valid = true; break; }
+    auto make_walk = [&]() {
+        Walk wk;
+        wk.first = cluster_id_x();
+        wk.step = cluster_count_x();
+        wk.n_items = p.n_items;
+        wk.n_entries = p.n_entries;
+        wk.items_per_class = p.items_per_class;
+        wk.step_e = (int)(wk.step % p.n_entries);
+        wk.step_bh = wk.step / p.n_entries;
+        wk.range = ctrl->range;
+        return wk;
     };
 
-    // Each warpgroup takes its register budget (the softmax threads keep 128 scores in registers)
-    // and then runs its role; the budgets only hold inside these branches.
-    if (warp >= kTmaWarp) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-      if (run && warp == kTmaWarp) {
+    if (run && warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer
         // Loads follow the order in which the tensor core consumes them: K(0) K(1) K(2), then
         // V(G), K(G+3) for every step, with the Q tile of an item just before its first K tile.
         // This CTA loads keys [64 rank, +64) of every K tile and value columns [64 rank, +64) of
         // every V tile.
         if (lane == 0) {
+            const uint32_t rank = cluster_ctarank();
+            const Walk wk = make_walk();
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
@@ -396,8 +398,8 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (qb) q_last1 = c.G + c.N - 1; else q_last0 = c.G + c.N - 1;
                     PAIR_TRACE(2, 21);
                 }
-                const int slot = (int)(c.G % kBufs);
-                if (!slot_wait(c.G - kBufs)) return false;       // S(G-3) has read this slot
+                const int slot = c.slot;
+                if (!slot_wait(c.G - kSlots)) return false;      // S(G-3) has read this slot
                 if (rank == 0) mbar_arrive_expect_tx(&ctrl->k_full[slot], 2 * kSlotBytes);
                 const uint32_t bar = leader_addr(&ctrl->k_full[slot]);
                 for (int sub = 0; sub < 2; ++sub)
@@ -407,8 +409,9 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 return true;
             };
             auto load_v = [&](const Cursor& c) {
-                const int slot = (int)(c.G % kBufs);
-                if (c.G >= kBufs && !slot_wait(c.G)) return false;   // PV(G-3) has read this slot
+                const int slot = c.slot;
+                // PV(G-3) has read this slot: event (G-3) + kBufs
+                if (c.G >= kSlots && !slot_wait(c.G - kSlots + kBufs)) return false;
                 if (rank == 0) mbar_arrive_expect_tx(&ctrl->v_full[slot], 2 * kSlotBytes);
                 tma_load_4d_pair(s_v + slot * kSlotBytes, &tm_v, leader_addr(&ctrl->v_full[slot]),
                                  (int)rank * 64, c.res, (c.n_lo + c.i) * kTile, (int)c.at.bh);
@@ -416,29 +419,31 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 return true;
             };
             Cursor kc, vc;
-            cursor_begin(kc);
-            cursor_begin(vc);
+            wk.cursor_begin(kc);
+            wk.cursor_begin(vc);
             bool ok = true;
-            for (int t = 0; t < kBufs && kc.valid && ok; ++t) {
+            for (int t = 0; t < kSlots && kc.valid && ok; ++t) {
                 ok = load_k(kc);
-                cursor_next(kc);
+                wk.cursor_next(kc);
             }
             while (vc.valid && ok) {
                 ok = load_v(vc);
-                cursor_next(vc);
+                wk.cursor_next(vc);
                 if (ok && kc.valid) {
                     ok = load_k(kc);
-                    cursor_next(kc);
+                    wk.cursor_next(kc);
                 }
             }
             // giving up: copies already issued may still be landing (some counted on the other
             // CTA's barriers); let them finish before either CTA can leave
             if (!ok) spin_cycles(400000);
         }
-      } else if (run && warp == kMmaWarp) {
+    } else if (run && warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer (even CTA)
         // The whole warp walks the loop on warp-uniform values; one elected lane issues.
-        if (rank == 0) {
+        if (cluster_ctarank() == 0) {
+            const Walk wk = make_walk();
+            const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc_qk = instr_desc_f16(fmt, 2 * kTile, kTile, 0);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, 2 * kTile, D, 1);
@@ -447,7 +452,7 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const uint32_t ev_own = smem_u32(&ctrl->ev[0]);
             const uint32_t ev_peer = map_to_cta(ev_own, 1);
             const uint32_t o_tmem = tmem_base + kOCol;
-            uint32_t k_ph = 0, v_ph = 0, p_ph = 0;     // one phase bit per slot
+            uint32_t k_ph = 0, v_ph = 0, p_ph = 0;     // one phase bit per slot / buffer
             bool ok = true;
             auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
                 const bool r = mbar_wait(bar, parity, status, code);
@@ -460,18 +465,18 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     mma_commit_pair(ev_peer + off);
                 }
             };
-            // S of the step at cursor c, into score buffer G mod 3
+            // S of the step at cursor c, into score buffer G mod 2
             auto issue_s = [&](const Cursor& c) {
                 const int qb = c.jq & 1;
                 if (c.i == 0 && !wait_all(&ctrl->q_full[qb], (uint32_t)(c.jq >> 1) & 1u, kErrQ)) return false;
-                const int slot = (int)(c.G % kBufs);
+                const int slot = c.slot;
                 const bool r = wait_all(&ctrl->k_full[slot], (k_ph >> slot) & 1u, kErrKFull);
                 k_ph ^= 1u << slot;
                 if (!r) return false;
                 tc_fence_after_sync();
                 const uint32_t q_base = q_addr + qb * kTileBytes;
                 const uint32_t b_base = k_addr + slot * kSlotBytes;
-                const uint32_t d_tmem = tmem_base + slot * kTile;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(c.G & 1) * kTile;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024);
@@ -481,23 +486,24 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 return true;
             };
             Cursor sc, pc;
-            cursor_begin(sc);
-            cursor_begin(pc);
+            wk.cursor_begin(sc);
+            wk.cursor_begin(pc);
             for (int t = 0; t < kBufs && ok; ++t) {
                 if (sc.valid) {
                     ok = issue_s(sc);
-                    cursor_next(sc);
+                    wk.cursor_next(sc);
                 }
                 if (ok) commit_event(t);
             }
             while (pc.valid && ok) {
-                const int slot = (int)(pc.G % kBufs);
+                const int slot = pc.slot;
+                const int buf = (int)(pc.G & 1);
                 ok = wait_all(&ctrl->v_full[slot], (v_ph >> slot) & 1u, kErrVFull);
                 v_ph ^= 1u << slot;
                 if (!ok) break;
                 PAIR_TRACE(1, 10);
-                ok = wait_all(&ctrl->p_ready[slot], (p_ph >> slot) & 1u, kErrPReady);
-                p_ph ^= 1u << slot;
+                ok = wait_all(&ctrl->p_ready[buf], (p_ph >> buf) & 1u, kErrPReady);
+                p_ph ^= 1u << buf;
                 if (!ok) break;
                 if (pc.i == 0 && pc.jq > 0) {      // the previous item's O has been read out
                     ok = wait_all(&ctrl->o_free, (uint32_t)(pc.jq - 1) & 1u, kErrOFree);
@@ -505,24 +511,27 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 tc_fence_after_sync();
                 PAIR_TRACE(1, 11);
-                // O += P V: P packed in the first 64 columns of the step's score buffer
+                // O_h += P_h V_h: the P of key half h is packed in the first 32 of the 64 score
+                // columns its threads consumed
                 {
                     const uint32_t b_base = v_addr + slot * kSlotBytes;
-                    const uint32_t a_tmem = tmem_base + slot * kTile;
+                    const uint32_t a_tmem = tmem_base + buf * kTile;
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk) {
+                        const int h = kk >> 2;
                         const uint64_t db = smem_desc_sw128(b_base + kk * 2048, kSlotBytes, 1024);
-                        if (lead) mma_ts_pair(o_tmem, a_tmem + kk * 8, db, idesc_pv, (pc.i > 0 || kk > 0) ? 1u : 0u);
+                        if (lead) mma_ts_pair(o_tmem + h * D, a_tmem + h * kHalf + (kk & 3) * 8, db, idesc_pv,
+                                              (pc.i > 0 || (kk & 3) > 0) ? 1u : 0u);
                     }
                 }
-                if (sc.valid) {                    // S(G+3) into the buffer PV(G) has just consumed
+                if (sc.valid) {                    // S(G+2) into the buffer PV(G) has just consumed
                     ok = issue_s(sc);
                     if (!ok) break;
-                    cursor_next(sc);
+                    wk.cursor_next(sc);
                 }
                 commit_event(pc.G + kBufs);
                 PAIR_TRACE(1, 12);
-                cursor_next(pc);
+                wk.cursor_next(pc);
             }
             if (!ok && lead) {
                 // let the tensor pipe drain before tensor memory is released
@@ -533,18 +542,16 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
             __syncwarp();
         }
-      }
-    } else if (warp < kEpiWarp) {
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-      if (run) {
+    } else if (run && warp < kEpiWarp) {
         // ------------------------------------------------------------------ softmax
-        // Thread = row.  The 128 scores of a step pass through the registers in two halves, A and
-        // B: while the exponentials of one half run on the special function unit, the other half
-        // (of this step or the next) is loaded, masked and its maximum taken, so the two phases
-        // overlap inside one warp.
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        const uint32_t o_addr = lane_addr + kOCol;
-        const int t = warp * 32 + lane;              // row of this thread within the CTA's tile
+        // Thread = (row, key half): 64 of the 128 scores of every step.
+        const uint32_t rank = cluster_ctarank();
+        const Walk wk = make_walk();
+        const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+        const int h = warp >> 2;                     // key half
+        const int t = (warp & 3) * 32 + lane;        // row of this thread within the CTA's tile
+        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t o_addr = lane_addr + kOCol + h * D;
         const float sc = p.scale_log2;
         const float2 sc2 = make_float2(sc, sc);
         const uint32_t p_ready_addr = leader_addr(&ctrl->p_ready[0]);
@@ -559,14 +566,14 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             return (int64_t)min(u, p.rows_v - 1) * p.stride + res;
         };
         ItemPos at, nx;
-        pos_begin(at);
+        wk.begin(at);
         float nx_lin, nx_tr, nx_nn;
         {
             int res, u;
             const int64_t row = own_row(at, res, u);
             nx_lin = __ldg(p.lin + row); nx_tr = __ldg(p.tr + row); nx_nn = __ldg(p.nnzs + row);
         }
-        for (; at.w < p.n_items; at = nx) {
+        for (; at.w < wk.n_items; at = nx) {
             const uint32_t rg = ctrl->range[at.e];
             const int n_lo = (int)(rg & 0xffffu), N = (int)(rg >> 16);
             int res, u_own;
@@ -574,211 +581,119 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             int my_a, my_n, row_start, row_nnz;
             row_band(p, res, nx_lin, nx_tr, u_own < p.rows_v ? nx_nn : 0.f, my_a, my_n, row_start, row_nnz);
             nx = at;
-            pos_next(nx);
-            if (nx.w < p.n_items) {      // next item's row: in flight during this item's steps
+            wk.next(nx);
+            if (nx.w < wk.n_items) {      // next item's row: in flight during this item's steps
                 int r2, u2;
                 const int64_t row = own_row(nx, r2, u2);
                 nx_lin = __ldg(p.lin + row); nx_tr = __ldg(p.tr + row); nx_nn = __ldg(p.nnzs + row);
             }
             float m_used = -INFINITY, l_sum = 0.f;
             int pending = -1;        // score buffer whose P has been stored but not yet handed over
-            bool started = false;    // an earlier step of this item had valid columns for this warp: O is live
-            bool a_ready = false;    // A holds the first half of the coming step, its maximum in mt_a
-            float mt_a = -INFINITY;
-            uint32_t A[kHalf], B[kHalf];
+            bool started = false;    // an earlier step of this item had valid columns for this warp: O_h is live
+            const int v_lo0 = my_a - n_lo * kTile - h * kHalf;
 
-            // valid columns [v_lo, v_hi) of this thread's row in step i, relative to the step's first key
-            auto step_cols = [&](int i, int& v_lo, int& v_hi, bool& warp_in, bool& lo_ok, bool& hi_ok) {
-                const int c0 = (n_lo + i) * kTile;
-                v_lo = my_a - c0;
-                v_hi = my_n > 0 ? my_a + my_n - c0 : INT_MIN;
-                warp_in = __any_sync(0xffffffffu, my_n > 0 && v_lo < kTile && v_hi > 0);
-                lo_ok = __all_sync(0xffffffffu, v_lo <= 0);
-                hi_ok = __all_sync(0xffffffffu, v_hi >= kTile);
-            };
             // P of the pending buffer is complete in tensor memory: tell the MMA warp
             auto hand_over = [&]() {
                 tmem_st_wait();
-                PAIR_TRACE(0, 13);
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(p_ready_addr + pending * 8);
                 pending = -1;
             };
-            // New running maximum from the maximum mt of the coming half.  Lazy: the reference m_used
-            // only moves when a row's maximum grows by more than 2^8, and then everything already
-            // accumulated under the old reference is scaled by corr: l_sum, O (PV(G-1) must have
-            // completed) and, when half_done, the first half of P(G) already stored in tensor memory.
-            auto new_max = [&](float mt, int64_t G, uint32_t s_addr, bool half_done, float2& acc0,
-                               float2& acc1) {
-                const float m_new = fmaxf(m_used, mt * sc);
-                const bool need = (m_new - m_used) > kRescaleThreshold;   // false when both are -inf
-                const float corr = need ? ex2(m_used - m_new) : 1.f;
-                if (need) m_used = m_new;
-                l_sum *= corr;
-                if (!__any_sync(0xffffffffu, need)) return true;
-                // sums of the step's first half, not yet in l_sum
-                acc0.x *= corr; acc0.y *= corr; acc1.x *= corr; acc1.y *= corr;
-                if (started) {
-                    bool r = event_wait(G - 1 + kBufs, kErrEvent);
-                    r = __all_sync(0xffffffffu, r);
-                    if (!r) return false;
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int ch = 0; ch < D / 16; ++ch) {
-                        uint32_t o[16];
-                        tmem_ld16(o_addr + ch * 16, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-                        tmem_st16(o_addr + ch * 16, o);
-                    }
-                }
-                if (half_done) {
-                    tmem_st_wait();      // the first half of P(G) was stored a moment ago
-#pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
-                        uint32_t w[16];
-                        tmem_ld16(s_addr + ch * 16, w);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float2 f = unpack2<T>(w[j]);
-                            w[j] = pack2<T>(f.x * corr, f.y * corr);
-                        }
-                        tmem_st16(s_addr + ch * 16, w);
-                    }
-                }
-                return true;
-            };
 
             for (int i = 0; i < N; ++i) {
                 const int64_t G = G0 + i;
-                const int slot = (int)(G % kBufs);
-                const uint32_t s_addr = lane_addr + slot * kTile;
-                int v_lo, v_hi;
-                bool warp_in, lo_ok, hi_ok;
-                step_cols(i, v_lo, v_hi, warp_in, lo_ok, hi_ok);
+                const int buf = (int)(G & 1);
+                const uint32_t s_addr = lane_addr + buf * kTile + h * kHalf;   // this thread's 64 scores
+                // valid columns [v_lo, v_lo + my_n) of the row, relative to this half's first key
+                const int v_lo = v_lo0 - i * kTile;
+                const bool warp_in = __any_sync(0xffffffffu, my_n > 0 && v_lo < kHalf && v_lo + my_n > 0);
+                const bool edge = !__all_sync(0xffffffffu, v_lo <= 0 && v_lo + my_n >= kHalf);
                 PAIR_TRACE(0, 1);
-                if (!a_ready) {
-                    ok = event_wait(G, kErrEvent);            // S(G) complete (and PV(G-3): the buffer is free)
-                    ok = __all_sync(0xffffffffu, ok);         // keep the warp together for the aligned tcgen05 ops
+                // The previous step's P is normally handed over a little later, under this step's
+                // load and maximum; but if this step's scores are not there yet, the tensor core is
+                // waiting for that very P (or for work that follows it): hand it over first.
+                if (!__all_sync(0xffffffffu, mbar_test_wait(&ctrl->ev[G & (kEvents - 1)], (uint32_t)(G >> 5) & 1u))) {
+                    if (pending >= 0) hand_over();
+                    ok = event_wait(G, kErrEvent);        // S(G) complete (and PV(G-2): the buffer is free)
+                    ok = __all_sync(0xffffffffu, ok);     // keep the warp together for the aligned tcgen05 ops
                     if (!ok) break;
-                    tc_fence_after_sync();
                 }
+                tc_fence_after_sync();
                 PAIR_TRACE(0, 2);
+                uint32_t r[kHalf];
                 if (!warp_in) {
-                    // none of this warp's rows reaches into this step (the other tile's does):
-                    // the pair MMA still multiplies these rows, so P must be zero
+                    // none of this warp's rows has a valid column here (another warp's does): the
+                    // pair MMA still multiplies these rows, so P must be zero
                     if (pending >= 0) hand_over();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) B[j] = 0u;
-                    tmem_st32(s_addr, B);
-                    tmem_st32(s_addr + 32, B);
-                    pending = slot;
-                    a_ready = false;
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    tmem_st32(s_addr, r);
+                    pending = buf;
                     continue;
                 }
-                if (!a_ready) {
-#ifndef SPLAT_ABL_NOLD
-                    tmem_ld32(s_addr, A);
-                    tmem_ld32(s_addr + 32, A + 32);
-                    tmem_ld_wait();
-#endif
-                    reg_fence64(A);
-                    mt_a = masked_max<0>(A, v_lo, v_hi, lo_ok, hi_ok);
-                }
+                tmem_ld32(s_addr, r);
+                tmem_ld32(s_addr + 32, r + 32);
+                tmem_ld_wait();
                 PAIR_TRACE(0, 3);
-                // ---- first half: exponentials of A; B is loaded, masked and its maximum taken
-#ifndef SPLAT_ABL_NOLD
-                tmem_ld32(s_addr + 64, B);
-                tmem_ld32(s_addr + 96, B + 32);
-#endif
-                if (pending >= 0) hand_over();   // the previous step's P has had time to land
+                const float mt = masked_max(r, v_lo, my_n, edge);
+                const float m_new = fmaxf(m_used, mt * sc);
+                const bool need = (m_new - m_used) > kRescaleThreshold;  // false when both are -inf
+                const float corr = need ? ex2(m_used - m_new) : 1.f;
+                if (need) m_used = m_new;
+                l_sum *= corr;
+                const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+                PAIR_TRACE(0, 4);
+                // the previous step's P has had the time of this step's load and maximum to land
+                if (pending >= 0) hand_over();
                 PAIR_TRACE(0, 9);
-                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-                ok = new_max(mt_a, G, s_addr, false, acc0, acc1);
-                if (!ok) break;
-                {
-                    const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-                    const float2 nm2 = make_float2(-m_eff, -m_eff);
-                    exp_part<T, 0, 16>(A, sc2, nm2, acc0, acc1);
-                    tmem_ld_wait();
-                    reg_fence64(B);
-                    const float mt_b = masked_max<1>(B, v_lo, v_hi, lo_ok, hi_ok);
-                    exp_part<T, 16, kHalf>(A, sc2, nm2, acc0, acc1);
-#ifndef SPLAT_ABL_NOST
-                    tmem_st32(s_addr, A);          // P of keys 0..63: 32 packed columns
-#endif
-                    PAIR_TRACE(0, 4);
-                    // ---- second half: exponentials of B; the next step's first half goes into A
-                    ok = new_max(mt_b, G, s_addr, true, acc0, acc1);
+                // lazy rescale of this half's accumulator (rare): some row's maximum moved by more
+                // than 2^8.  PV(G-1) may still be running: wait for its event first.
+                if (started && __any_sync(0xffffffffu, need)) {
+                    ok = event_wait(G - 1 + kBufs, kErrEvent);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
+                    tc_fence_after_sync();
+                    rescale_o(o_addr, corr);
                 }
-                a_ready = false;
-                int nv_lo = 0, nv_hi = 0;
-                bool n_lo_ok = true, n_hi_ok = true;
-                if (i + 1 < N) {
-                    bool n_in;
-                    step_cols(i + 1, nv_lo, nv_hi, n_in, n_lo_ok, n_hi_ok);
-                    const int64_t e = G + 1;
-                    const bool ready = mbar_test_wait(&ctrl->ev[e & (kEvents - 1)], (uint32_t)(e >> 5) & 1u);
-                    if (n_in && __all_sync(0xffffffffu, ready)) {
-                        tc_fence_after_sync();
-                        const uint32_t n_addr = lane_addr + (int)(e % kBufs) * kTile;
-#ifndef SPLAT_ABL_NOLD
-                        tmem_ld32(n_addr, A);
-                        tmem_ld32(n_addr + 32, A + 32);
-#endif
-                        a_ready = true;
-                    }
-                }
-                {
-                    const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-                    const float2 nm2 = make_float2(-m_eff, -m_eff);
-                    exp_part<T, 0, 16>(B, sc2, nm2, acc0, acc1);
-                    if (a_ready) {
-                        tmem_ld_wait();
-                        reg_fence64(A);
-                        mt_a = masked_max<0>(A, nv_lo, nv_hi, n_lo_ok, n_hi_ok);
-                    }
-                    exp_part<T, 16, kHalf>(B, sc2, nm2, acc0, acc1);
-#ifndef SPLAT_ABL_NOST
-                    tmem_st32(s_addr + 32, B);     // P of keys 64..127
-#endif
-                }
+                // probabilities, row sum, 16-bit pack in place
+                const float2 nm2 = make_float2(-m_eff, -m_eff);
+                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+                exp_half<T>(r, sc2, nm2, acc0, acc1);
                 l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
-                pending = slot;
-                started = true;      // from the next step on O holds this warp's rows of this item
+                tmem_st32(s_addr, r);          // P: 32 packed columns over the consumed scores
+                pending = buf;
+                started = true;
                 PAIR_TRACE(0, 5);
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (pending >= 0) hand_over();
             PAIR_TRACE(0, 6);
-            // row sums to the epilogue warps; the buffer was last used two items ago
+            // running maximum and sum to the epilogue warps; the buffer was last used two items ago
             const int par = n_item & 1, use = n_item >> 1;
             if (use > 0) {
                 ok = mbar_wait(&ctrl->l_free[par], (uint32_t)(use - 1) & 1u, status, kErrRowSum);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            ctrl->l_buf[par][t] = l_sum;
+            ctrl->ml_buf[par][h][t] = make_float2(m_used, l_sum);
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->l_full[par]);
             PAIR_TRACE(0, 7);
             G0 += N;
             ++n_item;
         }
-      }
-    } else {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
-      if (run) {
+    } else if (run && warp < kTmaWarp) {
         // ------------------------------------------------------------------ epilogue
-        // O / l for band rows, V[start] for single-element rows, zero otherwise.  Rows are staged
-        // in shared memory in the 128-byte-swizzled tile layout and leave through one tiled TMA
-        // store per 64-column half (rows past the end of the class are clipped by the tensor map).
+        // (a_0 O_0 + a_1 O_1) / (a_0 l_0 + a_1 l_1) for band rows, V[start] for single-element
+        // rows, zero otherwise.  Rows are staged in shared memory in the 128-byte-swizzled tile
+        // layout and leave through one tiled TMA store per 64-column half (rows past the end of the
+        // class are clipped by the tensor map).
         const int ew = warp - kEpiWarp;
+        const uint32_t rank = cluster_ctarank();
+        const Walk wk = make_walk();
+        const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
         const uint32_t o_addr = tmem_base + ((uint32_t)(ew * 32) << 16) + kOCol;
         const int t = ew * 32 + lane;
         const uint32_t o_free_addr = leader_addr(&ctrl->o_free);
@@ -793,14 +708,14 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             return (int64_t)min(u, p.rows_v - 1) * p.stride + res;
         };
         ItemPos at, nx;
-        pos_begin(at);
+        wk.begin(at);
         float nx_lin, nx_tr, nx_nn;
         {
             int res, block, u;
             const int64_t row = own_row(at, res, block, u);
             nx_lin = __ldg(p.lin + row); nx_tr = __ldg(p.tr + row); nx_nn = __ldg(p.nnzs + row);
         }
-        for (; at.w < p.n_items; at = nx) {
+        for (; at.w < wk.n_items; at = nx) {
             const uint32_t rg = ctrl->range[at.e];
             const int n_lo = (int)(rg & 0xffffu), N = (int)(rg >> 16);
             int res, block, u_own;
@@ -810,8 +725,8 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             row_band(p, res, nx_lin, nx_tr, row_exists ? nx_nn : 0.f, my_a, my_n, row_start, row_nnz);
             const int64_t bh = at.bh;
             nx = at;
-            pos_next(nx);
-            if (nx.w < p.n_items) {
+            wk.next(nx);
+            if (nx.w < wk.n_items) {
                 int r2, b2, u2;
                 const int64_t row = own_row(nx, r2, b2, u2);
                 nx_lin = __ldg(p.lin + row); nx_tr = __ldg(p.tr + row); nx_nn = __ldg(p.nnzs + row);
@@ -820,14 +735,21 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const int hi_tile = warp_max_i(my_n > 0 ? (my_a + my_n + kTile - 1) / kTile : 0);
             const int last_active = min(hi_tile, n_lo + N) - 1 - n_lo;
             PAIR_TRACE(3, 30);
-            // row sums of the item (the softmax warps are done with it)
+            // maxima and sums of the item (the softmax warps are done with it)
             const int par = n_item & 1, use = n_item >> 1;
             ok = mbar_wait(&ctrl->l_full[par], (uint32_t)use & 1u, status, kErrRowSum);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const float l_sum = ctrl->l_buf[par][t];
+            const float2 ml0 = ctrl->ml_buf[par][0][t], ml1 = ctrl->ml_buf[par][1][t];
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->l_free[par]);
+            // weights of the two key halves: a_h / (a_0 l_0 + a_1 l_1)
+            const float m = fmaxf(ml0.x, ml1.x);
+            const float a0 = ml0.x == -INFINITY ? 0.f : ex2(ml0.x - m);
+            const float a1 = ml1.x == -INFINITY ? 0.f : ex2(ml1.x - m);
+            const float l_sum = a0 * ml0.y + a1 * ml1.y;
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            const float w0 = a0 * inv, w1 = a1 * inv;
             // This warp's rows of O are final once the PV of its last step with valid columns has
             // completed; later steps of the item (the other tile's) add zeros to them.  A warp
             // without such a step still waits for the item's first PV: that MMA is only issued once
@@ -841,6 +763,29 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tc_fence_after_sync();
             }
             PAIR_TRACE(3, 31);
+            // O out of tensor memory first (merged, normalised, packed to 16 bits: 64 registers),
+            // so that the next item's first PV, which overwrites O, waits as little as possible
+            uint32_t packed[D / 2];
+            if (have_o) {  // warp-uniform
+#pragma unroll
+                for (int ch = 0; ch < D / 16; ++ch) {      // 16-column chunk of the row
+                    uint32_t r0[16], r1[16];
+                    tmem_ld16(o_addr + ch * 16, r0);
+                    tmem_ld16(o_addr + D + ch * 16, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2)
+                        packed[ch * 8 + (j >> 1)] = pack2<T>(
+                            __uint_as_float(r0[j]) * w0 + __uint_as_float(r1[j]) * w1,
+                            __uint_as_float(r0[j + 1]) * w0 + __uint_as_float(r1[j + 1]) * w1);
+                }
+            }
+            if (N > 0) {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(o_free_addr);
+            }
+            PAIR_TRACE(3, 33);
             // the staging buffer is free once the previous item's store has read it
             if (storer) {
                 tma_store_wait_read();
@@ -851,44 +796,26 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             if (!ok) break;
             {
                 const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
-                const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t r[64];
-                    if (have_o) {  // warp-uniform
-                        tmem_ld32(o_addr + half * 64, r);
-                        tmem_ld32(o_addr + half * 64 + 32, r + 32);
-                        tmem_ld_wait();
-                        reg_fence64(r);
-                    }
-                    if (half == 1 && N > 0) {      // O is in registers: the next item may overwrite it
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(o_free_addr);
-                    }
-#pragma unroll
-                    for (int c2 = 0; c2 < 2; ++c2) {
-                        const int ch = half * 2 + c2;      // 32-column chunk of the row
-                        uint4 out[4];
-                        if (row_nnz > 1 && have_o) {
-                            uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2)
-                                o32[j >> 1] = pack2<T>(__uint_as_float(r[c2 * 32 + j]) * inv,
-                                                       __uint_as_float(r[c2 * 32 + j + 1]) * inv);
-                        } else if (row_nnz == 1 && row_exists) {
-#pragma unroll
-                            for (int q4 = 0; q4 < 4; ++q4)
-                                out[q4] = *reinterpret_cast<const uint4*>(vrow + ch * 32 + q4 * 8);
-                        } else {
-#pragma unroll
-                            for (int q4 = 0; q4 < 4; ++q4) out[q4] = make_uint4(0, 0, 0, 0);
-                        }
-                        uint8_t* srow = s_stage + (ch >> 1) * kSubBytes + t * 128;
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    uint4 out[4];
+                    if (row_nnz > 1 && have_o) {
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4)
-                            *reinterpret_cast<uint4*>(srow + ((((ch & 1) * 4 + q4) ^ (t & 7)) << 4)) = out[q4];
+                            out[q4] = make_uint4(packed[ch * 16 + q4 * 4], packed[ch * 16 + q4 * 4 + 1],
+                                                 packed[ch * 16 + q4 * 4 + 2], packed[ch * 16 + q4 * 4 + 3]);
+                    } else if (row_nnz == 1 && row_exists) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4)
+                            out[q4] = *reinterpret_cast<const uint4*>(vrow + ch * 32 + q4 * 8);
+                    } else {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) out[q4] = make_uint4(0, 0, 0, 0);
                     }
+                    uint8_t* srow = s_stage + (ch >> 1) * kSubBytes + t * 128;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<uint4*>(srow + ((((ch & 1) * 4 + q4) ^ (t & 7)) << 4)) = out[q4];
                 }
             }
             fence_proxy_async_smem();
@@ -913,7 +840,6 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             ++n_item;
         }
         if (storer) tma_store_wait_read();
-      }
     }
 
     // ------------------------------------------------------------------ exit
@@ -922,7 +848,7 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     cluster_sync_all();      // nothing of either CTA is in flight towards the other any more
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
-        tmem_dealloc_pair(tmem_base, kTmemCols);
+        tmem_dealloc_pair(ctrl->tmem_base, kTmemCols);
     }
 }
 

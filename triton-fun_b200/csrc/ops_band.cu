@@ -296,17 +296,24 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0 && steps > 0) {
+        // (the whole warp walks the loop on warp-uniform values and one elected lane issues: a
+        // single lane in a divergent branch is issue-bound on tcgen05.mma)
+        if (steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc = instr_desc_f16(fmt, kTile, kStep, 0);
+            const bool lead = elect_one();
+            auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+                const bool r = mbar_wait(bar, parity, status, code);
+                return __all_sync(0xffffffffu, r) != 0;
+            };
             const uint32_t ring_addr = smem_u32(s_ring), q_base = smem_u32(s_q);
-            bool ok = mbar_wait(&ctrl->q_full, 0, status, kErrQ);
+            bool ok = wait_all(&ctrl->q_full, 0, kErrQ);
             uint32_t free_phase[2] = {0, 0};
             for (int k = klo; k < khi && ok; ++k) {
                 const int item = k - klo, b = k & 1;
-                ok = mbar_wait(&ctrl->full[item % kStages], (uint32_t)(item / kStages) & 1u, status, kErrFull);
+                ok = wait_all(&ctrl->full[item % kStages], (uint32_t)(item / kStages) & 1u, kErrFull);
                 if (ok && item >= 2) {   // the store warps have read the scores that were in this buffer
-                    ok = mbar_wait(&ctrl->freed[b], free_phase[b], status, kErrFree);
+                    ok = wait_all(&ctrl->freed[b], free_phase[b], kErrFree);
                     free_phase[b] ^= 1u;
                 }
                 if (!ok) break;
@@ -314,18 +321,21 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 OPS_TRACE(20);
                 const uint32_t b_base = ring_addr + (item % kStages) * L::kItemBytes;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    mma_ss(tmem_base + b * kStep,
-                           smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024),
-                           smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024),
-                           idesc, kk > 0);
-                mma_commit(&ctrl->empty[item % kStages]);
-                mma_commit(&ctrl->ready[b]);
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t da = smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024);
+                    if (lead) mma_ss(tmem_base + b * kStep, da, db, idesc, kk > 0);
+                }
+                if (lead) {
+                    mma_commit(&ctrl->empty[item % kStages]);
+                    mma_commit(&ctrl->ready[b]);
+                }
                 OPS_TRACE(21);
             }
             // let the tensor pipe drain before tensor memory is released
-            mma_commit(&ctrl->drain);
+            if (lead) mma_commit(&ctrl->drain);
             wait_quiet(&ctrl->drain, 0);
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------------ store warps
@@ -542,31 +552,41 @@ spmm_band_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0 && steps > 0) {
+        // (whole warp on warp-uniform values, one elected lane issues)
+        if (steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc = instr_desc_f16(fmt, kTile, D, 1);   // A K-major, B (V) MN-major
+            const bool lead = elect_one();
+            auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+                const bool r = mbar_wait(bar, parity, status, code);
+                return __all_sync(0xffffffffu, r) != 0;
+            };
             const uint32_t ring_addr = smem_u32(s_ring), p_base = smem_u32(s_p);
             bool ok = true;
             uint32_t ready_phase[2] = {0, 0};
             for (int k = klo; k < khi && ok; ++k) {
                 const int item = k - klo, b = k & 1;
-                ok = mbar_wait(&ctrl->full[item % kStages], (uint32_t)(item / kStages) & 1u, status, kErrFull);
-                if (ok) ok = mbar_wait(&ctrl->ready[b], ready_phase[b], status, kErrReady);
+                ok = wait_all(&ctrl->full[item % kStages], (uint32_t)(item / kStages) & 1u, kErrFull);
+                if (ok) ok = wait_all(&ctrl->ready[b], ready_phase[b], kErrReady);
                 if (!ok) break;
                 ready_phase[b] ^= 1u;
                 tc_fence_after_sync();
                 const uint32_t a_base = p_base + b * L::kPBytes;
                 const uint32_t b_base = ring_addr + (item % kStages) * L::kItemBytes;
 #pragma unroll
-                for (int kk = 0; kk < kStep / 16; ++kk)
-                    mma_ss(tmem_base, smem_desc_sw128(a_base + kk * 32, 16, 1024),
-                           smem_desc_sw128(b_base + kk * 2048, kStepBytesPerSub, 1024), idesc,
-                           (k > klo || kk > 0) ? 1u : 0u);
-                mma_commit(&ctrl->empty[item % kStages]);
-                mma_commit(&ctrl->freed[b]);
+                for (int kk = 0; kk < kStep / 16; ++kk) {
+                    const uint64_t da = smem_desc_sw128(a_base + kk * 32, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(b_base + kk * 2048, kStepBytesPerSub, 1024);
+                    if (lead) mma_ss(tmem_base, da, db, idesc, (k > klo || kk > 0) ? 1u : 0u);
+                }
+                if (lead) {
+                    mma_commit(&ctrl->empty[item % kStages]);
+                    mma_commit(&ctrl->freed[b]);
+                }
             }
-            mma_commit(&ctrl->drain);   // every MMA complete: O final, P tiles free for the staging
+            if (lead) mma_commit(&ctrl->drain);   // every MMA complete: O final, P tiles free for the staging
             wait_quiet(&ctrl->drain, 0);
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------------ P loaders + epilogue
