@@ -13,7 +13,11 @@ rank's heads.  Prints ONE JSON line on rank 0:
   e2e           the same metric through RegularAttention.forward_host: pinned host operands,
                 host->device and device->host copies inside the timed region
   roofline      the fused kernel against the measured dense bf16 peak
-  cpu_baseline  the C restatement of the reference kernels on the host cores, bounded sample
+  cpu_baseline  the C restatement of the reference kernels on the host cores, bounded sample; plus
+                (one GPU only) the dense-masked torch chain on configurations 1 and 2
+  other_configs (one GPU only) the fused kernel on configurations 2, 3 and 4, each timed for at
+                least half a second with its own clock record and roofline
+  check         one head of the timed output against the CPU oracle (outside the timed region)
 """
 from __future__ import annotations
 
@@ -38,6 +42,7 @@ UNIT = "TFLOP/s"
 
 #  cfg: (B, H, L, d, dtype name, pattern, p0, p1, input scale, seed, label)
 CONFIGS = {
+    1: (1, 2, 256, 32, "fp32", "causal_windowed", 31, 0, 1.0, 0, "cfg1 plumbing, causal window 32"),
     2: (4, 16, 4096, 64, "fp16", "causal_windowed", 255, 0, 1.0, 1, "cfg2 local causal window 256"),
     3: (2, 32, 8192, 128, "bf16", "strided", 64, 0, 1.0, 2, "cfg3 column stride 64"),
     4: (1, 32, 16384, 128, "bf16", "dilated", 512, 2, 0.5, 3, "cfg4 dilated window 512x2"),
@@ -167,6 +172,121 @@ def cpu_reference_sample(cfg, budget_s=20.0, max_heads=16):
     return flops / dt_s / 1e12, heads, dt_s, c_oracle.num_threads()
 
 
+def torch_dense_masked_baseline(cfgs=(1, 2), budget_s=12.0):
+    """The dense-masked torch chain (einsum, mask, softmax, matmul: what the reference's own
+    checker `truth` computes, SPLAT/r_sddmm.py:186-187) on the host cores, whole configurations."""
+    from oracle import acsr_oracle as ao
+    from oracle import attention_oracle as at
+    out = []
+    for cfg in cfgs:
+        B, H, L, d, dt, pat, p0, p1, spread, seed, label = CONFIGS[cfg]
+        meta = ao.metadata_from_pattern(KIND[pat], L, p0, p1, 16)
+        g = torch.Generator().manual_seed(seed)
+        q, k, v = ((torch.randn(B, H, L, d, generator=g) * spread).to(TORCH_DTYPE[dt]) for _ in range(3))
+        t0 = time.perf_counter()
+        at.attention_dense_masked(q, k.transpose(2, 3), v, meta, d ** -0.5)
+        secs = time.perf_counter() - t0
+        calls = 1
+        while secs < 0.2 and calls < 64:      # tiny configurations: repeat for a stable figure
+            t0 = time.perf_counter()
+            for _ in range(calls * 2):
+                at.attention_dense_masked(q, k.transpose(2, 3), v, meta, d ** -0.5)
+            secs = (time.perf_counter() - t0) / (calls * 2)
+            calls *= 2
+            if secs * calls > 0.5:
+                break
+        flops = 4.0 * nnz_per_head(cfg) * d * B * H
+        out.append({"workload": label, "ms_per_call": secs * 1e3, "value": flops / secs / 1e12, "unit": UNIT,
+                    "threads": torch.get_num_threads()})
+        budget_s -= secs
+        if budget_s < 0:
+            break
+    return out
+
+
+def ncu_traffic(cfg, heads, path):
+    """DRAM bytes per launch of the fused kernel from the ncu captures summarised under
+    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum), scaled by the head count, with the
+    capture it came from.  None if the kernel sources changed after the capture."""
+    meta_path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if path != "band" or not os.path.exists(meta_path):
+        return None, None
+    with open(meta_path) as f:
+        rec = json.load(f)
+    entry = rec["configs"].get(str(cfg))
+    if entry is None:
+        return None, None
+    import hashlib
+    h = hashlib.sha1()
+    for name in rec["kernel_sources"]:
+        with open(os.path.join(ROOT, name), "rb") as f:
+            h.update(f.read())
+    if h.hexdigest() != rec["kernel_sources_sha1"]:
+        return None, "kernel sources changed since the capture of " + rec["captured"]
+    return entry["bytes"] / entry["heads"] * heads, f"ncu capture of {rec['captured']}: {entry['what']}"
+
+
+def time_config(cfg, dev, min_seconds=0.5, max_launches=20000):
+    """The fused kernel on one of the smaller configurations, whole configuration on this GPU,
+    launches repeated until the timed region spans min_seconds (clock samples every 20 ms)."""
+    import r_attention
+    import acsr_helpers as ah
+    import splat_native as n
+    B, H, L, d, dt, pat, p0, p1, spread, seed, label = CONFIGS[cfg]
+    dtype = TORCH_DTYPE[dt]
+    heads = B * H
+    attn = r_attention.RegularAttention(1, L, heads, d, ah.PatternMask(KIND[pat], L, p0, p1), 16, 16, dev,
+                                        dtype, scale=d ** -0.5, path=n.PATH_BAND)
+    nnz = int(attn.nnzs.double().sum().item())
+    q, k, v = make_inputs(cfg, 0, heads, dev)
+    kt = k.transpose(2, 3)
+    for _ in range(20):
+        attn([q, kt, v])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(50):
+        attn([q, kt, v])
+    e1.record()
+    torch.cuda.synchronize()
+    est = e0.elapsed_time(e1) / 50
+    launches = int(min(max_launches, max(200, min_seconds * 1e3 / est * 1.1)))
+    clocks = ClockSampler(dev.index).start()
+    time.sleep(0.3)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(launches + 1)]
+    torch.cuda.synchronize()
+    clocks.mark_begin()
+    ev[0].record()
+    for i in range(launches):
+        attn([q, kt, v])
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    clocks.mark_end()
+    clocks.stop()
+    attn.check_status()
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(launches))
+    mean_ms = ev[0].elapsed_time(ev[-1]) / launches
+    peaks = measured_peaks()
+    flops = 4.0 * nnz * d * heads
+    bytes_alg = 4.0 * L * d * q.element_size() * heads
+    t_flop, t_hbm = flops / (peaks["tflops"] * 1e12), bytes_alg / (peaks["hbm_gbs"] * 1e9)
+    traffic, prov = ncu_traffic(cfg, heads, "band")
+    if t_flop >= t_hbm:
+        ach = flops / (mean_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"]}
+    else:
+        ach = bytes_alg / (mean_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
+    roof.update({"traffic": traffic, "traffic_source": prov, "peak_source": peaks["source"]})
+    out = {"workload": label, "dtype": dt, "launches": launches, "ms": mean_ms, "ms_median": per[len(per) // 2],
+           "ms_best": per[0], "value": flops / (mean_ms * 1e-3) / 1e12, "unit": UNIT, "roofline": roof,
+           "clocks": clocks.summary(), "l2": "L2 flushed by the launch itself: inputs + outputs = %.0f MB per launch"
+           % (bytes_alg / 1e6)}
+    del attn, q, k, v
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_reference(args):
     """The reference arm: the reference's algorithm on the host cores (C restatement; the Python +
     Triton reference itself has no compiled form and is not present where this runs)."""
@@ -187,7 +307,9 @@ def run_reference(args):
     sample = f"{heads} of {B * H} heads per step ({secs:.2f} s), fp32, S and P materialised"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3,
+        "steps": args.steps, "warmup": args.warmup,
+        # a step of this arm is a SAMPLE of heads; the step time is scaled to all heads
+        "ms_per_step": secs * 1e3 * (B * H) / heads, "sample_heads": heads, "sample_ms": secs * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": label, "B": B, "H": H, "L": L, "d": d,
                                         "pattern": pat, "p0": p0, "p1": p1},
@@ -263,7 +385,7 @@ def run_ours(args):
     clocks.mark_end()
     clocks.stop()
     attn.check_status()
-    per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    per_launch = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
     ms_total = ev[0].elapsed_time(ev[-1])
     ms_step = ms_total / args.steps
     t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
@@ -271,6 +393,26 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step_max = float(t.item())
     value = flops_per_head * total_heads / (ms_step_max * 1e-3) / 1e12
+
+    # ---------------------------------------------------------------- result check, one head
+    check = None
+    if rank == 0 and not args.no_check:
+        from oracle import acsr_oracle as ao
+        from oracle import attention_oracle as at
+        out = attn([q, kt, v])
+        torch.cuda.synchronize()
+        meta = ao.metadata_from_pattern(KIND[pat], L, p0, p1, 16)
+        hsel = heads - 1                                   # the last head of this rank's shard
+        ref = at.attention_acsr(q[:, hsel:hsel + 1].cpu(), k[:, hsel:hsel + 1].cpu().transpose(2, 3),
+                                v[:, hsel:hsel + 1].cpu(), meta, meta["trailing_dim"], scale)
+        got = out[:, hsel:hsel + 1].float().cpu()
+        err = (got - ref).abs()
+        tol = {"fp32": (1e-4, 1e-4)}.get(dt, (2e-2, 1e-2))
+        check = {"against": "oracle.attention_oracle.attention_acsr (fp32, CPU), one head of the timed output",
+                 "head": begin + hsel, "max_abs_err": float(err.max()),
+                 "within_tolerance": bool((err <= tol[0] + tol[1] * ref.abs()).all()),
+                 "tolerance": f"abs {tol[0]} + rel {tol[1]}"}
+        del out, ref, got, err
 
     # ---------------------------------------------------------------- end to end, host operands
     e2e = None
@@ -312,7 +454,32 @@ def run_ours(args):
             n.attention_fused(q1, k1.transpose(2, 3), v1, o1, attn.sTod_linear_transformations,
                               attn.sTod_translations, attn.nnzs, scale, attn.path, attn.plan)
             assert torch.equal(o1.cpu(), host[3][:, :1]), "forward_host disagrees with forward"
+        # what the copies alone cost: the same pinned buffers through the same staging, no kernel
+        def copies_only():
+            st = attn._host_stage
+            c = st["chunk"]
+            for i in range(-(-heads // c)):
+                buf = st["bufs"][i % 2]
+                for key, src in (("q", host[0]), ("k", host[1]), ("v", host[2])):
+                    buf[key][:, :c].copy_(src[:, :c], non_blocking=True)
+                host[3][:, :c].copy_(buf["o"][:, :c], non_blocking=True)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        copies_only()
+        c1.record()
+        barrier()
+        tc = torch.tensor([c0.elapsed_time(c1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        copy_bytes = 4 * heads * L * d * q.element_size() * world
+        copy_gbs = copy_bytes / (float(tc.item()) * 1e-3) / 1e9
+        e2e_gbs = copy_bytes / (float(te.item()) * 1e-3) / 1e9
         e2e = {"value": flops_per_head * total_heads / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT,
+               "copy_ceiling_gbs": copy_gbs, "achieved_copy_gbs": e2e_gbs,
+               "frac_of_copy_ceiling": e2e_gbs / copy_gbs,
+               "copy_ceiling": "host<->device copies of the same pinned buffers on one stream, no kernel, "
+                               "all ranks at once (aggregate GB/s, both directions)",
                "h2d_bytes_per_step": 3 * heads * L * d * q.element_size() * world,
                "d2h_bytes_per_step": heads * L * d * q.element_size() * world,
                "ms_per_step": float(te.item()), "steps": e2e_steps,
@@ -325,11 +492,22 @@ def run_ours(args):
         val, h, secs, threads = cpu_reference_sample(cfg, budget_s=args.cpu_budget)
         cpu = {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                "sample": f"{h} of {total_heads} heads ({secs:.1f} s) of the same workload, fp32, "
-                         "three kernels with S and P materialised"}
+                         "three kernels with S and P materialised",
+               "host_cpus": os.cpu_count(),
+               "torch_dense_masked": torch_dense_masked_baseline()}
+
+    # ---------------------------------------------------------------- the smaller configurations
+    other = None
+    if rank == 0 and world == 1 and not args.no_other and cfg == 5 and args.path == "band":
+        del q, k, v, kt
+        torch.cuda.empty_cache()
+        other = [time_config(c, dev) for c in (2, 3, 4)]
+        q = torch.empty(1, dtype=dtype, device=dev)     # element size for the figures below
 
     if rank == 0:
         peaks = measured_peaks()
         launch_ms = statistics.mean(per_launch)
+        launch_ms_median, launch_ms_best = per_launch[len(per_launch) // 2], per_launch[0]
         achieved = flops_per_head * heads / (launch_ms * 1e-3) / 1e12
         bytes_alg = 4.0 * L * d * q.element_size() * heads
         if unfused:   # S written and read, P written and read, on top of Q, K, V, O
@@ -344,17 +522,15 @@ def run_ours(args):
             gbs = bytes_alg / (launch_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"]}
-        # DRAM traffic per launch from the ncu captures summarised under profiles/
-        # (dram__bytes_read.sum + dram__bytes_write.sum).  Configuration 5 was captured on 16 of its
-        # 512 heads (520.0 MB) and is scaled by the head count: traffic grows in proportion, every
-        # head being independent.  Configurations 2-4 were captured at full size.
-        ncu_traffic_per_head = {5: 520.0e6 / 16, 2: 117.5e6 / 64, 3: 515.1e6 / 64, 4: 519.1e6 / 32}
-        traffic = ncu_traffic_per_head[cfg] * heads if args.path == "band" else None
-        roof.update({"traffic": traffic, "traffic_unit": "bytes per launch (ncu capture scaled by heads, see profiles/)",
+        traffic, traffic_source = ncu_traffic(cfg, heads, args.path)
+        roof.update({"traffic": traffic, "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, "
+                                                         "ncu capture scaled by heads)",
+                     "traffic_source": traffic_source,
                      "kernel": "sddmm + softmax + spmm (three launches)" if unfused else
                                ("attention_band_kernel" if args.path == "band" else "attention_rows_kernel"),
                      "peak_source": peaks["source"],
-                     "peak_kind": "burst", "launch_ms": launch_ms,
+                     "peak_kind": "burst", "launch_ms": launch_ms, "launch_ms_median": launch_ms_median,
+                     "launch_ms_best": launch_ms_best,
                      "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"])
                      if tensor_bound and peaks.get("tflops_sustained") else None,
                      "algorithmic_gflop_per_launch": flops_per_head * heads / 1e9,
@@ -368,7 +544,9 @@ def run_ours(args):
                        "parallelism": f"(batch,head) sharded over {world} GPU(s), no collective",
                        "l2": "inputs larger than L2 (per-GPU Q+K+V = %.0f MB)" % (3 * heads * L * d * q.element_size() / 1e6),
                        "path": args.path},
+            "ms_per_step_median": launch_ms_median, "ms_per_step_best": launch_ms_best,
             "e2e": e2e, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks.summary(),
+            "check": check, "other_configs": other,
             "gpu_launches": args.steps * world * (3 if unfused else 1), "metadata_build_ms": metadata_ms,
         }
         print(json.dumps(line), flush=True)
@@ -389,6 +567,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the oracle comparison of one head")
+    ap.add_argument("--no-other", action="store_true", help="skip configurations 2-4 (one GPU, configuration 5 only)")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--heads", type=int, default=0,
                     help="profiling aid: run only the first N (batch, head) pairs of the workload")

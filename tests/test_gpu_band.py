@@ -115,11 +115,13 @@ def test_auto_path_takes_operands_the_band_path_cannot():
     acsr = ah.create_acsr(ah.create_causal_windowed_mask(L, 63), 16, 0)
     meta = ao.metadata_from_pattern(ao.PATTERN_CAUSAL_WINDOWED, L, 63, 0, 16)
     torch.manual_seed(3)
-    pool = torch.randn(3, L * d + 8, device="cuda").to(torch.bfloat16)
-    # views that start one element (2 bytes) into their allocation
-    q, k, v = (pool[i, 1:1 + L * d].view(1, 1, L, d) for i in range(3))
-    o = torch.empty(L * d + 8, dtype=torch.bfloat16, device="cuda")[1:1 + L * d].view(1, 1, L, d)
-    assert q.data_ptr() % 16 != 0
+    pool = torch.randn(2, L * d + 8, device="cuda").to(torch.bfloat16)
+    # Q and K views that start one element (2 bytes) into their allocation; V and O stay aligned
+    # (the general fused kernel reads V and writes O in 16-byte vectors)
+    q, k = (pool[i, 1:1 + L * d].view(1, 1, L, d) for i in range(2))
+    v = torch.randn(1, 1, L, d, device="cuda").to(torch.bfloat16)
+    o = torch.empty_like(v)
+    assert q.data_ptr() % 16 != 0 and k.data_ptr() % 16 != 0
     with pytest.raises(RuntimeError):
         n.attention_fused(q, k.transpose(2, 3), v, o, acsr[2], acsr[3], acsr[4], d ** -0.5, n.PATH_BAND)
     import warnings
