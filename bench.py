@@ -456,13 +456,22 @@ def run_ours(args):
             assert torch.equal(o1.cpu(), host[3][:, :1]), "forward_host disagrees with forward"
         # what the copies alone cost: the same pinned buffers through the same staging, no kernel
         def copies_only():
+            # the same traffic as one e2e step, host->device and device->host on their own
+            # streams as forward_host runs them, without the kernels and their dependencies
             st = attn._host_stage
             c = st["chunk"]
+            cur = torch.cuda.current_stream(dev)
+            st["s_in"].wait_stream(cur)
+            st["s_out"].wait_stream(cur)
             for i in range(-(-heads // c)):
                 buf = st["bufs"][i % 2]
-                for key, src in (("q", host[0]), ("k", host[1]), ("v", host[2])):
-                    buf[key][:, :c].copy_(src[:, :c], non_blocking=True)
-                host[3][:, :c].copy_(buf["o"][:, :c], non_blocking=True)
+                with torch.cuda.stream(st["s_in"]):
+                    for key, src in (("q", host[0]), ("k", host[1]), ("v", host[2])):
+                        buf[key][:, :c].copy_(src[:, :c], non_blocking=True)
+                with torch.cuda.stream(st["s_out"]):
+                    host[3][:, :c].copy_(buf["o"][:, :c], non_blocking=True)
+            cur.wait_stream(st["s_in"])
+            cur.wait_stream(st["s_out"])
         barrier()
         c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         c0.record()
@@ -478,8 +487,9 @@ def run_ours(args):
         e2e = {"value": flops_per_head * total_heads / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT,
                "copy_ceiling_gbs": copy_gbs, "achieved_copy_gbs": e2e_gbs,
                "frac_of_copy_ceiling": e2e_gbs / copy_gbs,
-               "copy_ceiling": "host<->device copies of the same pinned buffers on one stream, no kernel, "
-                               "all ranks at once (aggregate GB/s, both directions)",
+               "copy_ceiling": "the step's host->device and device->host copies alone (same pinned buffers, the "
+                               "two directions on their own streams, no kernel), all ranks at once; aggregate "
+                               "GB/s over both directions",
                "h2d_bytes_per_step": 3 * heads * L * d * q.element_size() * world,
                "d2h_bytes_per_step": heads * L * d * q.element_size() * world,
                "ms_per_step": float(te.item()), "steps": e2e_steps,

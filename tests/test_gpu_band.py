@@ -32,7 +32,9 @@ def band_variant(request, monkeypatch):
     return request.param
 
 
-def _run(kind, L, p0, p1, d, dtype, seed, BH=(1, 3), scale=None, spread=1.0):
+def _run(kind, L, p0, p1, d, dtype, seed, BH=(1, 3), scale=None, spread=1.0, kt_contiguous=False):
+    """kt_contiguous: pass K^T as a contiguous (B,H,d,L) tensor, the layout the reference's kernels
+    index (SPLAT/r_sddmm.py:24-37), instead of the transposed view of a (B,H,L,d) tensor."""
     import acsr_helpers as ah
     import splat_native as n
     torch.manual_seed(seed)
@@ -42,8 +44,10 @@ def _run(kind, L, p0, p1, d, dtype, seed, BH=(1, 3), scale=None, spread=1.0):
     q, k, v = (torch.randn(B, H, L, d).mul_(spread).to(dtype) for _ in range(3))
     scale = d ** -0.5 if scale is None else scale
     out = torch.full((B, H, L, d), float("nan"), dtype=dtype, device="cuda")
-    n.attention_fused(q.cuda(), k.cuda().transpose(2, 3), v.cuda(), out, acsr[2], acsr[3], acsr[4],
-                      scale, n.PATH_BAND)
+    kt = k.cuda().transpose(2, 3)
+    if kt_contiguous:
+        kt = kt.contiguous()
+    n.attention_fused(q.cuda(), kt, v.cuda(), out, acsr[2], acsr[3], acsr[4], scale, n.PATH_BAND)
     n.check_status_word(0)
     ref = at.attention_acsr(q, k.transpose(2, 3), v, meta, meta["trailing_dim"], scale)
     return out, ref
@@ -62,6 +66,24 @@ def test_band_patterns(d, dtype):
     for i, (kind, L, p0, p1) in enumerate(PATTERNS):
         out, ref = _run(kind, L, p0, p1, d, dtype, 100 + i)
         assert_close(out, ref, dtype, f"pattern {(kind, L, p0, p1)} d={d}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [128, 64])
+def test_band_contiguous_kt(d, dtype):
+    """The reference's own K^T layout, contiguous (B,H,d,L), on the tensor-core path: every
+    stride-1 pattern of the list (strided and dilated patterns take that layout on the CUDA-core
+    path only and are refused here)."""
+    import splat_native as n
+    for i, (kind, L, p0, p1) in enumerate(PATTERNS):
+        if L % 8 != 0:
+            continue
+        if kind in (ao.PATTERN_STRIDED, ao.PATTERN_DILATED):
+            with pytest.raises(RuntimeError):
+                _run(kind, L, p0, p1, d, dtype, 300 + i, kt_contiguous=True)
+            continue
+        out, ref = _run(kind, L, p0, p1, d, dtype, 300 + i, kt_contiguous=True)
+        assert_close(out, ref, dtype, f"contiguous K^T, pattern {(kind, L, p0, p1)} d={d}")
 
 
 def test_band_unscaled_scores_need_the_running_max():
@@ -96,9 +118,16 @@ def test_band_path_refuses_what_it_cannot_do():
     q = torch.randn(1, 1, L, d, device="cuda").to(torch.bfloat16)
     o = torch.empty_like(q)
     kt_contig = q.transpose(2, 3).contiguous()
-    with pytest.raises(RuntimeError):      # contiguous K^T has no band path
-        n.attention_fused(q, kt_contig, q, o, acsr[2], acsr[3], acsr[4], 1.0, n.PATH_BAND)
-    n.attention_fused(q, kt_contig, q, o, acsr[2], acsr[3], acsr[4], 1.0, n.PATH_AUTO)  # falls back
+    # contiguous K^T is fine for a stride-1 pattern ...
+    n.attention_fused(q, kt_contig, q, o, acsr[2], acsr[3], acsr[4], 1.0, n.PATH_BAND)
+    # ... but a pattern with stride > 1 takes that layout on the CUDA-core kernels only
+    acsr_d = ah.create_acsr(ah.create_dilated_mask(L, 20, 2), 16, 0)
+    with pytest.raises(RuntimeError):
+        n.attention_fused(q, kt_contig, q, o, acsr_d[2], acsr_d[3], acsr_d[4], 1.0, n.PATH_BAND)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        n.attention_fused(q, kt_contig, q, o, acsr_d[2], acsr_d[3], acsr_d[4], 1.0, n.PATH_AUTO)  # falls back
     q32 = q.float()
     with pytest.raises(RuntimeError):      # fp32 has no band path
         n.attention_fused(q32, q32.transpose(2, 3), q32, torch.empty_like(q32), acsr[2], acsr[3],

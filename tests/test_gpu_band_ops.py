@@ -71,6 +71,30 @@ def test_band_ops_patterns(d, dtype):
         _check_ops(acsr, meta, L, d, dtype, 200 + i, f"{(kind, L, p0, p1)} d={d}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [128, 64])
+def test_band_sddmm_contiguous_kt(d, dtype):
+    """The reference's K^T layout, contiguous (B,H,d,L) (SPLAT/r_sddmm.py:24-37), through the
+    tensor-core SDDMM for the stride-1 patterns; bit-identical to the transposed-view layout."""
+    import splat_native as n
+    for i, (kind, L, p0, p1) in enumerate(PATTERNS):
+        if kind in (ao.PATTERN_STRIDED, ao.PATTERN_DILATED) or L % 8 != 0:
+            continue
+        acsr, meta = _meta(kind, L, p0, p1)
+        T = int(meta["trailing_dim"])
+        torch.manual_seed(400 + i)
+        q, k = (torch.randn(1, 3, L, d).to(dtype) for _ in range(2))
+        s_ref = at.sddmm_acsr(q, k.transpose(2, 3), meta, T)
+        outs = []
+        for kt in (k.cuda().transpose(2, 3).contiguous(), k.cuda().transpose(2, 3)):
+            s_band = torch.full((1, 3, L, T), float("nan"), dtype=dtype, device="cuda")
+            n.sddmm(q.cuda(), kt, s_band, acsr[2], acsr[3], acsr[4], T, n.PATH_BAND)
+            n.check_status_word(0)
+            outs.append(s_band)
+        assert_close(outs[0], s_ref, dtype, f"sddmm band, contiguous K^T {(kind, L, p0, p1)} d={d}")
+        assert torch.equal(outs[0], outs[1])
+
+
 def test_band_ops_rows_without_a_band():
     """Empty rows, a row with one non-zero away from column 0, odd trailing dimension."""
     import acsr_helpers as ah

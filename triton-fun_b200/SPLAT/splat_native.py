@@ -294,7 +294,10 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = 
         raise ValueError("sddmm: inconsistent operand shapes or dtypes")
     if tuple(output.shape) != (B, H, L, trailing_dim):
         raise ValueError(f"sddmm: output must have shape {(B, H, L, trailing_dim)}")
-    if _band_candidate(x, path) and ksk == 1 and ksc == d and ksb == n_cols * d:
+    # K layouts the tensor-core kernel reads: the transposed view of a contiguous (B,H,L,d) tensor, or
+    # the reference's contiguous (B,H,d,L) K^T (the library checks the rest)
+    k_layout_ok = ksb == n_cols * d and ((ksk == 1 and ksc == d) or (ksc == 1 and ksk == n_cols))
+    if _band_candidate(x, path) and k_layout_ok:
         _raise_if_gave_up(dev)
         plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
         with torch.cuda.device(dev):
@@ -368,8 +371,9 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
 
 def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.0,
                     path: int = PATH_AUTO, plan=None) -> None:
-    """q, v, output (B,H,L,d) contiguous; kt (B,H,d,L) -- contiguous, or the transposed view of a
-    contiguous (B,H,L,d) tensor (required by the band path)."""
+    """q, v, output (B,H,L,d) contiguous; kt (B,H,d,L) -- contiguous (the reference's layout), or
+    the transposed view of a contiguous (B,H,L,d) tensor.  The tensor-core path takes both (the
+    contiguous one for stride-1 patterns)."""
     dev = q.device
     _contig(q, "q"); _contig(v, "v"); _contig(output, "output")
     B, H, L, d = q.shape

@@ -22,6 +22,11 @@
 // S(k0), S(k0+1), then for every k: PV(k), S(k+2).
 // Warps: 0-3 softmax/epilogue of tile A, 4-7 of tile B (thread = row = TMEM lane), 8 = TMA producer,
 // 9 / 10 = MMA issuers of tile A / B (9 also owns tensor memory), 11 idle.
+// K operand layouts.  K-major: K rows of d contiguous elements (the transposed view of a (BH, L, d)
+// array); ring tiles hold [keys][128 bytes of d] per 64-element chunk of d.  Key-major
+// (Params::kt_major): the reference's own contiguous (BH, d, L) K^T; ring tiles then hold
+// [d][128 bytes = 64 keys] per 64-key chunk, fetched through a tensor map over (L, d, BH), and the
+// QK MMA takes B as an MN-major operand exactly as the PV MMA takes V.
 // Rows with exactly one non-zero are described by the metadata as column `start` whatever their
 // class, so they are excluded from the band and written as O[i] = V[start_i]; rows with no
 // non-zero are written as zero.
@@ -75,6 +80,7 @@ struct Params {
     int64_t n_rows;    // L
     int rows_v;        // L / stride: rows of one residue class
     int stride;
+    int kt_major;      // 1: K is given as a contiguous (BH, d, L) array (keys innermost); stride 1 only
     float scale_log2;  // softmax scale * log2(e), > 0
 };
 
@@ -266,6 +272,12 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                     mbar_arrive_expect_tx(&ctrl->kv_full[stage], L::kTileBytes);
                     const CUtensorMap* tm = which == 0 ? &tm_k : &tm_v;
+                    if (which == 0 && p.kt_major) {
+                        for (int c = 0; c < kTile / 64; ++c)      // 64-key chunks of [d][64 keys]
+                            tma_load_4d(s_ring + stage * L::kTileBytes + c * (D * 128), tm,
+                                        &ctrl->kv_full[stage], n * kTile + c * 64, 0, (int)bh, 0);
+                        continue;
+                    }
                     for (int sub = 0; sub < L::kSub; ++sub)
                         tma_load_4d(s_ring + stage * L::kTileBytes + sub * kSubBytes, tm,
                                     &ctrl->kv_full[stage], sub * 64, res, n * kTile, (int)bh);
@@ -289,7 +301,7 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (any_work) {
             const bool lead = elect_one();
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, 0);
+            const uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, p.kt_major ? 1u : 0u);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
             const uint32_t ring_addr = smem_u32(s_ring);
             const uint32_t q_base = smem_u32(s_q) + x * L::kTileBytes;
@@ -310,13 +322,15 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             auto release = [&](int item) { commit(&ctrl->kv_empty[stage_of(item)]); };
             // S(k): 64 keys = rows [64(k&1), +64) of K tile k/2, into score buffer k&1
             auto issue_s = [&](int k) {
-                const uint32_t b_base = ring_addr + stage_of(2 * ((k >> 1) - n_lo)) * L::kTileBytes +
-                                        (k & 1) * (kStep * 128);
+                const uint32_t t_base = ring_addr + stage_of(2 * ((k >> 1) - n_lo)) * L::kTileBytes;
+                // K-major: key rows [64 (k&1), +64) of each d chunk; key-major: chunk k&1 of [d][64 keys]
+                const uint32_t b_base = t_base + (k & 1) * (p.kt_major ? D * 128 : kStep * 128);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kSubBytes + (kk & 3) * 32;
                     const uint64_t da = smem_desc_sw128(q_base + off, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(b_base + off, 16, 1024);
+                    const uint64_t db = p.kt_major ? smem_desc_sw128(b_base + kk * 2048, D * 128, 1024)
+                                                   : smem_desc_sw128(b_base + off, 16, 1024);
                     if (lead) mma_ss(s_tmem + (k & 1) * kStep, da, db, idesc_qk, kk > 0);
                 }
             };
@@ -696,6 +710,11 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     }
                     mbar_arrive_expect_tx(&ctrl->kv_full[stage], L::kItemBytes);
                     const CUtensorMap* tm = which == 0 ? &tm_k : &tm_v;
+                    if (which == 0 && p.kt_major) {       // one [d][64 keys] block
+                        tma_load_4d(s_ring + stage * L::kItemBytes, tm, &ctrl->kv_full[stage], k * kStep, 0,
+                                    (int)bh, 0);
+                        continue;
+                    }
                     for (int sub = 0; sub < L::kSub; ++sub)
                         tma_load_4d(s_ring + stage * L::kItemBytes + sub * kStepBytesPerSub, tm,
                                     &ctrl->kv_full[stage], sub * 64, res, k * kStep, (int)bh);
@@ -714,7 +733,7 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // (whole warp on warp-uniform values, one elected lane issues: see the paired kernel)
         if (steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, 0);
+            const uint32_t idesc_qk = instr_desc_f16(fmt, kTile, kStep, p.kt_major ? 1u : 0u);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, kTile, D, 1);
             const bool lead = elect_one();
             const uint32_t ring_addr = smem_u32(s_ring), q_base = smem_u32(s_q);
@@ -732,7 +751,9 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = p.kt_major
+                        ? smem_desc_sw128(b_base + kk * 2048, D * 128, 1024)
+                        : smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024);
                     if (lead) mma_ss(tmem_base + (k & 1) * kStep, da, db, idesc_qk, kk > 0);
                 }
             };
@@ -969,6 +990,25 @@ bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int
     return rc == CUDA_SUCCESS;
 }
 
+// Contiguous (BH, d, L) K^T viewed as (L, d, BH, 1); box (64 keys, d, 1, 1), 128B swizzle: one
+// [d][64 keys] block per copy.  (also used by the pair kernel and the band SDDMM)
+bool make_map_kt(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_cols,
+                 int64_t d) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)n_cols, (cuuint64_t)d, (cuuint64_t)bh, 1};
+    const cuuint64_t strides[3] = {(cuuint64_t)(n_cols * 2), (cuuint64_t)(d * n_cols * 2),
+                                   (cuuint64_t)(bh * d * n_cols * 2)};
+    const cuuint32_t box[4] = {64, (cuuint32_t)d, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult rc = fn(map, dtype == SPLAT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
 #ifdef SPLAT_BAND_TRACE
 static long long* g_trace = nullptr;
 #endif
@@ -1017,9 +1057,9 @@ static int32_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 
 }  // namespace band
 
-int32_t attention_pair(const void* q, const void* k, const void* v, void* o, const float* lin,
-                       const float* tr, const float* nnzs, int64_t bh, int64_t n_rows, int64_t stride,
-                       float scale, int32_t dtype, int32_t* status_word, int max_pairs,
+int32_t attention_pair(const void* q, const void* k, int kt_major, const void* v, void* o,
+                       const float* lin, const float* tr, const float* nnzs, int64_t bh, int64_t n_rows,
+                       int64_t stride, float scale, int32_t dtype, int32_t* status_word, int max_pairs,
                        cudaStream_t st);
 
 int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
@@ -1035,13 +1075,19 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     if (d != 64 && d != 128) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (!(scale > 0.f)) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (n_rows != n_cols || n_rows == 0 || bh == 0) return SPLAT_ERR_UNSUPPORTED_SHAPE;
-    if (ksk != 1 || ksc != d || ksb != n_cols * d) return SPLAT_ERR_UNSUPPORTED_SHAPE;
+    // K layouts the tensor-core kernels read: rows of d contiguous elements (the transposed view of a
+    // (BH, L, d) array), or the reference's contiguous (BH, d, L) K^T (checked further down: only
+    // for stride-1 patterns, and its row pitch L must be a multiple of 16 bytes)
+    const bool k_major = ksk == 1 && ksc == d && ksb == n_cols * d;
+    const bool kt_major = ksc == 1 && ksk == n_cols && ksb == n_cols * d;
+    if (!k_major && !kt_major) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     // plan: {max_nnz, stride_min, stride_max, misaligned, n_single, max_col+1, n_empty, n_multi}
     const int64_t stride = plan[7] > 0 ? plan[1] : 1;
     if (plan[7] > 0 && plan[1] != plan[2]) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (plan[3] != 0 || stride < 1 || stride > 65535 || n_rows % stride != 0)
         return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (plan[5] > n_cols || bh > 65535 || n_rows > INT32_MAX) return SPLAT_ERR_UNSUPPORTED_SHAPE;
+    if (!k_major && (stride != 1 || n_cols % 8 != 0)) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SPLAT_ERR_MISALIGNED;
 
     // Kernel choice.  1: one Q tile per CTA (two CTAs per SM), for classes with a single row tile or
@@ -1057,8 +1103,8 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     if (variant == 3 && d == 128) {
         int max_pairs = 0;
         if (const char* e = getenv("SPLAT_B200_PAIR_MAX")) max_pairs = atoi(e);
-        const int32_t rc = attention_pair(q, k, v, o, lin, tr, nnzs, bh, n_rows, stride, scale, dtype,
-                                          status_word, max_pairs, st);
+        const int32_t rc = attention_pair(q, k, kt_major ? 1 : 0, v, o, lin, tr, nnzs, bh, n_rows, stride,
+                                          scale, dtype, status_word, max_pairs, st);
         if (rc != SPLAT_ERR_UNSUPPORTED_SHAPE) return rc;
     }
     if (variant == 3) variant = 2;
@@ -1066,11 +1112,13 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     const int kv_box = single ? band::kStep : band::kTile;
     CUtensorMap mq, mk, mv, mo;
     if (!band::make_map(&mq, q, dtype, bh, n_rows, d, stride) ||
-        !band::make_map(&mk, k, dtype, bh, n_rows, d, stride, kv_box) ||
+        !(kt_major ? band::make_map_kt(&mk, k, dtype, bh, n_cols, d)
+                   : band::make_map(&mk, k, dtype, bh, n_rows, d, stride, kv_box)) ||
         !band::make_map(&mv, v, dtype, bh, n_rows, d, stride, kv_box) ||
         !band::make_map(&mo, o, dtype, bh, n_rows, d, stride))
         return SPLAT_ERR_DRIVER;
     band::Params prm;
+    prm.kt_major = kt_major ? 1 : 0;
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.o = o; prm.status = status_word;
     prm.n_rows = n_rows; prm.rows_v = (int)(n_rows / stride); prm.stride = (int)stride;
     prm.scale_log2 = scale * kLog2e;

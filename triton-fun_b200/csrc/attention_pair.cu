@@ -26,7 +26,7 @@
 // tensor-memory columns hold two score buffers (step G uses buffer G mod 2), O_0 and O_1; the
 // tensor core runs up to two steps ahead of the softmax warps, also into the next item: issue
 // order S(0) S(1), then per step PV(G), S(G+2).  Operand halves are loaded by each CTA for itself
-// with plain TMA loads (no multicast); the byte counts of both CTAs land on barriers of the even
+// with plain TMA loads into its own shared memory; the byte counts of both CTAs land on barriers of the even
 // CTA, whose MMA warp is the only consumer.
 //
 // Progress of the tensor core is published as numbered EVENTS: event e is one tcgen05.commit per
@@ -56,6 +56,8 @@ namespace splat {
 namespace band {
 bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_rows,
               int64_t d, int64_t stride, int box_rows);
+bool make_map_kt(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_cols,
+                 int64_t d);
 }
 
 namespace pair {
@@ -99,6 +101,7 @@ struct Params {
     int rows_v;            // L / stride: rows of one residue class
     int stride;
     int items_per_class;   // ceil(rows_v / 256)
+    int kt_major;          // 1: K is a contiguous (BH, d, L) array (keys innermost); stride 1 only
     int n_entries;         // stride * items_per_class <= kMaxEntries
     int64_t n_items;       // n_entries * bh
     float scale_log2;      // softmax scale * log2(e), > 0
@@ -402,9 +405,13 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (!slot_wait(c.G - kSlots)) return false;      // S(G-3) has read this slot
                 if (rank == 0) mbar_arrive_expect_tx(&ctrl->k_full[slot], 2 * kSlotBytes);
                 const uint32_t bar = leader_addr(&ctrl->k_full[slot]);
-                for (int sub = 0; sub < 2; ++sub)
-                    tma_load_4d_pair(s_k + slot * kSlotBytes + sub * kKHalfSub, &tm_k, bar, sub * 64, c.res,
-                                     (c.n_lo + c.i) * kTile + (int)rank * 64, (int)c.at.bh);
+                if (p.kt_major)      // one [d][64 keys] block (see attention_band.cu on K layouts)
+                    tma_load_4d_pair(s_k + slot * kSlotBytes, &tm_k, bar, (c.n_lo + c.i) * kTile + (int)rank * 64,
+                                     0, (int)c.at.bh, 0);
+                else
+                    for (int sub = 0; sub < 2; ++sub)
+                        tma_load_4d_pair(s_k + slot * kSlotBytes + sub * kKHalfSub, &tm_k, bar, sub * 64, c.res,
+                                         (c.n_lo + c.i) * kTile + (int)rank * 64, (int)c.at.bh);
                 PAIR_TRACE(2, 22);
                 return true;
             };
@@ -445,7 +452,7 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const Walk wk = make_walk();
             const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t idesc_qk = instr_desc_f16(fmt, 2 * kTile, kTile, 0);
+            const uint32_t idesc_qk = instr_desc_f16(fmt, 2 * kTile, kTile, p.kt_major ? 1u : 0u);
             constexpr uint32_t idesc_pv = instr_desc_f16(fmt, 2 * kTile, D, 1);
             const bool lead = elect_one();
             const uint32_t q_addr = smem_u32(s_q), k_addr = smem_u32(s_k), v_addr = smem_u32(s_v);
@@ -480,7 +487,9 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(b_base + (kk >> 2) * kKHalfSub + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = p.kt_major
+                        ? smem_desc_sw128(b_base + kk * 2048, kSlotBytes, 1024)
+                        : smem_desc_sw128(b_base + (kk >> 2) * kKHalfSub + (kk & 3) * 32, 16, 1024);
                     if (lead) mma_ss_pair(d_tmem, da, db, idesc_qk, kk > 0);
                 }
                 return true;
@@ -918,9 +927,9 @@ static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 // already validated the operands; d must be 128.  Returns SPLAT_ERR_UNSUPPORTED_SHAPE (nothing
 // launched) for sequence lengths beyond what its range table or its float32 index arithmetic
 // cover.  max_pairs > 0 limits the number of resident pairs (bring-up and tests).
-int32_t attention_pair(const void* q, const void* k, const void* v, void* o, const float* lin,
-                       const float* tr, const float* nnzs, int64_t bh, int64_t n_rows, int64_t stride,
-                       float scale, int32_t dtype, int32_t* status_word, int max_pairs,
+int32_t attention_pair(const void* q, const void* k, int kt_major, const void* v, void* o,
+                       const float* lin, const float* tr, const float* nnzs, int64_t bh, int64_t n_rows,
+                       int64_t stride, float scale, int32_t dtype, int32_t* status_word, int max_pairs,
                        cudaStream_t st) {
     const int64_t d = pair::D;
     const int64_t rows_v = n_rows / stride;
@@ -929,13 +938,15 @@ int32_t attention_pair(const void* q, const void* k, const void* v, void* o, con
         return SPLAT_ERR_UNSUPPORTED_SHAPE;
     CUtensorMap mq, mk, mv, mo;
     if (!band::make_map(&mq, q, dtype, bh, n_rows, d, stride, pair::kTile) ||
-        !band::make_map(&mk, k, dtype, bh, n_rows, d, stride, 64) ||
+        !(kt_major ? band::make_map_kt(&mk, k, dtype, bh, n_rows, d)
+                   : band::make_map(&mk, k, dtype, bh, n_rows, d, stride, 64)) ||
         !band::make_map(&mv, v, dtype, bh, n_rows, d, stride, pair::kTile) ||
         !band::make_map(&mo, o, dtype, bh, n_rows, d, stride, pair::kTile))
         return SPLAT_ERR_DRIVER;
     pair::Params prm;
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.status = status_word;
     prm.trace = pair::g_trace;
+    prm.kt_major = kt_major;
     prm.n_rows = n_rows;
     prm.rows_v = (int)rows_v;
     prm.stride = (int)stride;

@@ -30,6 +30,8 @@ using namespace tc;
 // defined in attention_band.cu
 bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_rows,
               int64_t d, int64_t stride, int box_rows);
+bool make_map_kt(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_cols,
+                 int64_t d);
 
 namespace ops {
 
@@ -61,6 +63,7 @@ struct Params {
     int stride;
     int trailing_dim;
     int direct;          // sddmm: S is 16-byte aligned, full runs may be stored straight from registers
+    int kt_major;        // sddmm: K is a contiguous (BH, d, L) array (keys innermost), stride 1 only
 };
 
 #ifdef SPLAT_OPS_TRACE
@@ -284,9 +287,13 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint32_t parity = ((uint32_t)(item / kStages) & 1u) ^ 1u;
                 if (!mbar_wait(&ctrl->empty[stage], parity, status, kErrEmpty)) { ok = false; break; }
                 mbar_arrive_expect_tx(&ctrl->full[stage], L::kItemBytes);
-                for (int sub = 0; sub < L::kSub; ++sub)
-                    tma_load_4d(s_ring + stage * L::kItemBytes + sub * kStepBytesPerSub, &tm_k,
-                                &ctrl->full[stage], sub * 64, res, k * kStep, (int)bh);
+                if (p.kt_major)      // one [d][64 keys] block (K layouts: see attention_band.cu)
+                    tma_load_4d(s_ring + stage * L::kItemBytes, &tm_k, &ctrl->full[stage], k * kStep, 0,
+                                (int)bh, 0);
+                else
+                    for (int sub = 0; sub < L::kSub; ++sub)
+                        tma_load_4d(s_ring + stage * L::kItemBytes + sub * kStepBytesPerSub, &tm_k,
+                                    &ctrl->full[stage], sub * 64, res, k * kStep, (int)bh);
             }
             if (!ok) {   // leave only after the copies already issued have landed
                 wait_quiet(&ctrl->q_full, 0);
@@ -300,7 +307,7 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // single lane in a divergent branch is issue-bound on tcgen05.mma)
         if (steps > 0) {
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t idesc = instr_desc_f16(fmt, kTile, kStep, 0);
+            const uint32_t idesc = instr_desc_f16(fmt, kTile, kStep, p.kt_major ? 1u : 0u);
             const bool lead = elect_one();
             auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
                 const bool r = mbar_wait(bar, parity, status, code);
@@ -323,7 +330,9 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = smem_desc_sw128(q_base + (kk >> 2) * kSubBytes + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = p.kt_major
+                        ? smem_desc_sw128(b_base + kk * 2048, D * 128, 1024)
+                        : smem_desc_sw128(b_base + (kk >> 2) * kStepBytesPerSub + (kk & 3) * 32, 16, 1024);
                     if (lead) mma_ss(tmem_base + b * kStep, da, db, idesc, kk > 0);
                 }
                 if (lead) {
@@ -435,8 +444,10 @@ sddmm_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (nnz == 1) {
                     float acc = 0.f;
                     const T* qr = qg + (row0 + real) * D;
-                    const T* kr = kg + (row0 + start) * D;
-                    for (int c = lane; c < D; c += 32) acc += to_f<T>(qr[c]) * to_f<T>(kr[c]);
+                    // K[bh][start][c]: rows of d elements, or column `start` of the (d, L) array
+                    const int64_t k0 = p.kt_major ? row0 * D + start : (row0 + start) * D;
+                    const int64_t kc = p.kt_major ? p.n_rows : 1;
+                    for (int c = lane; c < D; c += 32) acc += to_f<T>(qr[c]) * to_f<T>(kg[k0 + c * kc]);
                     acc = warp_sum(acc);
                     if (lane == 0) dst[0] = from_f<T>(acc);
                 }
@@ -772,13 +783,17 @@ extern "C" int32_t splat_sddmm_band(const void* q, const void* k, int64_t k_stri
     const int32_t rc = ops::band_applies(plan_i32, bh, n_rows, n_cols, d, trailing_dim, dtype, &stride);
     if (rc != SPLAT_OK) return rc;
     if (!q || !k || !s_out || !sTod_lin || !sTod_tr || !nnzs || !status_word) return SPLAT_ERR_BAD_ARG;
-    if (k_stride_k != 1 || k_stride_col != d || k_stride_bh != n_cols * d) return SPLAT_ERR_UNSUPPORTED_SHAPE;
+    const bool k_major = k_stride_k == 1 && k_stride_col == d && k_stride_bh == n_cols * d;
+    const bool kt_major = k_stride_col == 1 && k_stride_k == n_cols && k_stride_bh == n_cols * d;
+    if (!k_major && !(kt_major && stride == 1 && n_cols % 8 == 0)) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (!ops::aligned16(q) || !ops::aligned16(k)) return SPLAT_ERR_MISALIGNED;
     CUtensorMap mq, mk;
     if (!make_map(&mq, q, dtype, bh, n_rows, d, stride, ops::kTile) ||
-        !make_map(&mk, k, dtype, bh, n_rows, d, stride, ops::kStep))
+        !(k_major ? make_map(&mk, k, dtype, bh, n_rows, d, stride, ops::kStep)
+                  : make_map_kt(&mk, k, dtype, bh, n_cols, d)))
         return SPLAT_ERR_DRIVER;
     ops::Params prm;
+    prm.kt_major = k_major ? 0 : 1;
 #ifdef SPLAT_OPS_TRACE
     prm.trace = ops::g_trace;
 #endif
@@ -817,6 +832,7 @@ extern "C" int32_t splat_spmm_band(const void* p, const void* v, void* o, const 
     prm.status = status_word; prm.n_rows = n_rows; prm.rows_v = (int)(n_rows / stride);
     prm.stride = (int)stride; prm.trailing_dim = (int)trailing_dim;
     prm.direct = 0;
+    prm.kt_major = 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == SPLAT_BF16)
         return d == 128 ? ops::launch_spmm<__nv_bfloat16, 128>(mv, mo, prm, bh, st)

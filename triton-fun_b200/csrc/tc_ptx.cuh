@@ -253,7 +253,7 @@ __device__ __forceinline__ void tmem_st_wait() {
 // CTA pairs (cluster of two CTAs driving one tcgen05 "cta_group::2" instruction stream).
 //
 // Both CTAs of a pair allocate tensor memory together, each stages its own operand halves in its
-// own shared memory with ordinary (non-multicast) TMA loads, one thread of the even CTA issues the
+// own shared memory with ordinary TMA loads (every CTA fetches what it needs itself), one thread of the even CTA issues the
 // MMAs for both SMs, and completion is signalled to a barrier in each CTA with one commit per CTA.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -291,7 +291,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 
 // TMA load into this CTA's shared memory whose completion bytes are counted on an mbarrier that
-// may live in the other CTA of the pair (bar_cluster_addr from map_to_cta).  No multicast.
+// may live in the other CTA of the pair (bar_cluster_addr from map_to_cta).  The data goes to this CTA only.
 __device__ __forceinline__ void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map,
                                                  uint32_t bar_cluster_addr, int c0, int c1, int c2,
                                                  int c3) {
