@@ -362,6 +362,9 @@ def run_ours(args):
     flops_per_head = 4.0 * nnz * d
     q, k, v = make_inputs(cfg, begin, end, dev)
     kt = k.transpose(2, 3)
+    if args.kt == "contiguous":      # the reference's own layout: a contiguous (B,H,d,L) tensor
+        kt = kt.contiguous()
+        args.no_e2e = True           # forward_host streams row-major K
 
     def barrier():
         torch.cuda.synchronize()
@@ -553,7 +556,7 @@ def run_ours(args):
                        "p1": p1, "softmax_scale": "1/sqrt(d)", "heads_per_gpu": heads, "heads_total": total_heads,
                        "parallelism": f"(batch,head) sharded over {world} GPU(s), no collective",
                        "l2": "inputs larger than L2 (per-GPU Q+K+V = %.0f MB)" % (3 * heads * L * d * q.element_size() / 1e6),
-                       "path": args.path},
+                       "path": args.path, "kt_layout": args.kt},
             "ms_per_step_median": launch_ms_median, "ms_per_step_best": launch_ms_best,
             "e2e": e2e, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks.summary(),
             "check": check, "other_configs": other,
@@ -574,6 +577,8 @@ def main():
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
     ap.add_argument("--path", default="band", choices=["band", "generic", "auto", "unfused"],
                     help="fused kernel choice, or 'unfused': the reference's three launches (SDDMM, softmax, SpMM)")
+    ap.add_argument("--kt", default="view", choices=["view", "contiguous"],
+                    help="K^T operand: transposed view of a (B,H,L,d) tensor, or a contiguous (B,H,d,L) tensor")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
