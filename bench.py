@@ -208,11 +208,15 @@ def ncu_traffic(cfg, heads, path):
     """DRAM bytes per launch of the fused kernel from the ncu captures summarised under
     profiles/ (dram__bytes_read.sum + dram__bytes_write.sum), scaled by the head count, with the
     capture it came from.  None if the kernel sources changed after the capture."""
-    meta_path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    meta_path = os.path.join(ROOT, "profiles", "dram_traffic.md")
     if path != "band" or not os.path.exists(meta_path):
         return None, None
     with open(meta_path) as f:
-        rec = json.load(f)
+        text = f.read()
+    try:
+        rec = json.loads(text.split("```json", 1)[1].split("```", 1)[0])
+    except (IndexError, ValueError):
+        return None, "profiles/dram_traffic.md holds no readable record"
     entry = rec["configs"].get(str(cfg))
     if entry is None:
         return None, None
