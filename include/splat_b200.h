@@ -217,6 +217,17 @@ int32_t splat_spmm_band(const void* p, const void* v, void* o, const float* sTod
  * usable.  No counterpart in the reference. */
 int32_t splat_selftest_bounded_wait(int32_t* status_word, int64_t limit_cycles, void* stream);
 
+/* Checked-index mode of the CUDA-core kernels (splat_sddmm, splat_spmm and the CUDA-core path of
+ * splat_attention_fused).  While a device int32 is registered, every dense column the kernels
+ * derive from the row metadata (start + j * stride) is compared with [0, n_cols) before it is
+ * dereferenced; a column outside the range is clamped to the nearest valid one and the kernel's
+ * code is stored in the word if it still holds 0 (71 = SDDMM, 72 = SpMM, 73 = fused).  Null (the
+ * default) switches the comparison off.  The setting is process-wide and is read at each launch;
+ * the word must stay valid until the launches that saw it have completed.  Counterpart in the
+ * reference: none (its kernels index K and V by raw pointer arithmetic,
+ * SPLAT/r_sddmm.py:24-37, SPLAT/r_spmm.py:24-38). */
+int32_t splat_debug_check_indices(int32_t* status_word);
+
 #ifdef __cplusplus
 }
 #endif

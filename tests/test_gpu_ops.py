@@ -219,3 +219,74 @@ def test_empty_batch_and_rows_without_nonzeros():
     n.softmax(s0, s0, acsr[4], T)
     n.spmm(s0, q0, out0, acsr[2], acsr[3], acsr[4], T)
     torch.cuda.synchronize()
+
+
+def test_checked_index_mode_clamps_and_reports():
+    """Checked-index mode of the CUDA-core kernels.  The metadata below names columns up to 110 while
+    n_cols = 64 is passed in; K and V are allocated with 128 columns, so every address the kernels
+    can form, clamped or not, lies inside the allocation.  With the mode on, columns >= n_cols must
+    be read as column n_cols - 1 and the kernel's code must be left in the registered word; with it
+    off the columns are used as they are and the word stays 0."""
+    import ctypes
+    import splat_native as n
+    dev = torch.device("cuda", 0)
+    rows, n_cols, n_alloc, d, T = 64, 64, 128, 32, 48
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(1, 1, rows, d, generator=g).to(dev)
+    k = torch.randn(1, 1, n_alloc, d, generator=g).to(dev)
+    v = torch.randn(1, 1, n_alloc, d, generator=g).to(dev)
+    p_in = torch.rand(1, 1, rows, T, generator=g).to(dev)
+    lin = torch.ones(rows, device=dev)
+    tr = torch.arange(rows, dtype=torch.float32, device=dev)          # start_i = i, stride 1
+    nnzs = torch.full((rows,), float(T), device=dev)
+    cols = torch.arange(rows, device=dev)[:, None] + torch.arange(T, device=dev)[None, :]   # up to 110
+    word = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    f32 = n.dtype_code(torch.float32)
+    scale = d ** -0.5
+
+    def reference(c):
+        s = torch.einsum("rd,rtd->rt", q[0, 0], k[0, 0][c])
+        o_spmm = torch.einsum("rt,rtd->rd", p_in[0, 0], v[0, 0][c])
+        o_fused = torch.einsum("rt,rtd->rd", torch.softmax(s * scale, dim=-1), v[0, 0][c])
+        return s, o_spmm, o_fused
+
+    def run():
+        s_out = torch.empty(1, 1, rows, T, device=dev)
+        o1 = torch.empty(1, 1, rows, d, device=dev)
+        o2 = torch.empty(1, 1, rows, d, device=dev)
+        results = []
+        for call in ("sddmm", "spmm", "fused"):
+            word.zero_()
+            if call == "sddmm":
+                rc = n._lib.splat_sddmm(q.data_ptr(), k.data_ptr(), n_alloc * d, d, 1, s_out.data_ptr(),
+                                        lin.data_ptr(), tr.data_ptr(), nnzs.data_ptr(), 1, rows, n_cols, d, T,
+                                        f32, st)
+            elif call == "spmm":
+                rc = n._lib.splat_spmm(p_in.data_ptr(), v.data_ptr(), o1.data_ptr(), lin.data_ptr(),
+                                       tr.data_ptr(), nnzs.data_ptr(), 1, rows, n_cols, d, T, f32, st)
+            else:
+                rc = n._lib.splat_attention_fused(q.data_ptr(), k.data_ptr(), n_alloc * d, d, 1, v.data_ptr(),
+                                                  o2.data_ptr(), lin.data_ptr(), tr.data_ptr(), nnzs.data_ptr(),
+                                                  1, rows, n_cols, d, ctypes.c_float(scale), f32,
+                                                  n.PATH_GENERIC, None, word.data_ptr(), st)
+            assert rc == 0, (call, rc)
+            torch.cuda.synchronize()
+            results.append(int(word.item()))
+        return s_out[0, 0], o1[0, 0], o2[0, 0], results
+
+    try:
+        assert n._lib.splat_debug_check_indices(word.data_ptr()) == 0
+        s_c, o1_c, o2_c, codes = run()
+    finally:
+        assert n._lib.splat_debug_check_indices(None) == 0
+    assert codes == [71, 72, 73], codes
+    ref = reference(cols.clamp(max=n_cols - 1))
+    for got, want, name in zip((s_c, o1_c, o2_c), ref, ("sddmm", "spmm", "fused")):
+        assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), f"checked {name}: {(got - want).abs().max().item()}"
+    s_u, o1_u, o2_u, codes = run()
+    assert codes == [0, 0, 0], codes
+    ref = reference(cols)
+    for got, want, name in zip((s_u, o1_u, o2_u), ref, ("sddmm", "spmm", "fused")):
+        assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), f"unchecked {name}: {(got - want).abs().max().item()}"
+    assert (s_c - s_u).abs().max().item() > 1e-3   # the clamp changed what was read

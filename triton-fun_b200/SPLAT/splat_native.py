@@ -44,6 +44,7 @@ SIGNATURES = {
     "splat_spmm_band": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp,
                         _vp],
     "splat_selftest_bounded_wait": [_vp, _i64, _vp],
+    "splat_debug_check_indices": [_vp],
     "splat_attention_noalloc": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                 _i64, _i64, _i64, _f32, _i32, _vp],
 }
@@ -225,6 +226,25 @@ def _refresh_mirror(dev: torch.device) -> None:
         m["host"].copy_(status_word(dev), non_blocking=True)
 
 
+_INDEX_CODES = {71: "sddmm", 72: "spmm", 73: "fused"}
+
+
+def check_indices(dev, on: bool = True) -> None:
+    """Checked-index mode of the CUDA-core kernels: columns derived from the metadata are clamped to
+    [0, n_cols) and a code (71 SDDMM, 72 SpMM, 73 fused) is left in the device's status word, which
+    check_status_word() reads.  SPLAT_B200_DEBUG switches it on for every CUDA-core launch."""
+    dev = resolve_device(dev)
+    check(_lib.splat_debug_check_indices(status_word(dev).data_ptr() if on else None),
+          "splat_debug_check_indices")
+
+
+def _debug_before(dev) -> bool:
+    if not os.environ.get("SPLAT_B200_DEBUG"):
+        return False
+    check_indices(dev, True)
+    return True
+
+
 def check_status_word(dev) -> None:
     """Synchronises the device; raises if a band kernel reported a timed-out wait (and clears it)."""
     dev = resolve_device(dev)
@@ -236,6 +256,9 @@ def check_status_word(dev) -> None:
         if m is not None:
             torch.cuda.synchronize(dev)
             m["host"].zero_()
+        if code in _INDEX_CODES:
+            raise RuntimeError(f"checked-index mode: a column derived from the row metadata lies outside "
+                               f"[0, n_cols) in the {_INDEX_CODES[code]} kernel (code {code})")
         raise RuntimeError(f"band kernel gave up on a device-side wait (code {code}): "
                            f"{status_string(-5)}")
 
@@ -316,11 +339,14 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = 
         raise RuntimeError("sddmm: the band path does not apply to these operands")
     if x.dtype != torch.float32 and x.numel() > 0:
         _warn_cuda_core_16bit("sddmm")
+    debug = _debug_before(dev)
     with torch.cuda.device(dev):
         check(_lib.splat_sddmm(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
                                _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
                                _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, trailing_dim,
                                dtype_code(x.dtype), _stream(dev)), "splat_sddmm")
+    if debug:
+        check_status_word(dev)
 
 
 def softmax(x, output, nnzs, trailing_dim: int, scale: float = 1.0) -> None:
@@ -362,11 +388,14 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
         raise RuntimeError("spmm: the band path does not apply to these operands")
     if x.dtype != torch.float32 and x.numel() > 0:
         _warn_cuda_core_16bit("spmm")
+    debug = _debug_before(dev)
     with torch.cuda.device(dev):
         check(_lib.splat_spmm(x.data_ptr(), y.data_ptr(), output.data_ptr(),
                               _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
                               _f32_vec(nnzs, L, "nnzs"), B * H, L, n_cols, d, T,
                               dtype_code(x.dtype), _stream(dev)), "splat_spmm")
+    if debug:
+        check_status_word(dev)
 
 
 def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.0,
@@ -392,6 +421,7 @@ def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.
         _raise_if_gave_up(dev)
     sw = status_word(dev)
     ran = ctypes.c_int32(0)
+    _debug_before(dev)
     with torch.cuda.device(dev):
         check(_lib.splat_attention_fused_ex(
             q.data_ptr(), kt.data_ptr(), ksb, ksc, ksk, v.data_ptr(), output.data_ptr(),

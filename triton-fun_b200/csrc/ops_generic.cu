@@ -19,6 +19,23 @@ namespace splat {
 
 constexpr int kWarpsPerBlock = 4;
 
+// Checked-index mode (splat_debug_check_indices): while a word is registered, every dense column
+// these kernels derive from the row metadata is compared with [0, n_cols); a column outside it is
+// clamped to the nearest valid one before it is dereferenced and the kernel's code is recorded in
+// the word (the first code stays).  Off (null) the comparison is skipped.
+static int32_t* g_index_check = nullptr;
+enum : int32_t { kIndexSddmm = 71, kIndexSpmm = 72, kIndexFused = 73 };
+
+__device__ __forceinline__ int64_t slot_col(const RowAffine& ra, int j, int64_t n_cols, int32_t* check,
+                                            int32_t code) {
+    int64_t col = (int64_t)ra.start + (int64_t)j * ra.stride;
+    if (check != nullptr && (col < 0 || col >= n_cols)) {
+        atomicCAS(check, 0, code);
+        col = col < 0 ? 0 : n_cols - 1;
+    }
+    return col;
+}
+
 // ---------------------------------------------------------------------------------------------
 // dot(Q row in shared memory, K[col, :])
 // ---------------------------------------------------------------------------------------------
@@ -56,7 +73,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 sddmm_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t ksb, int64_t ksc,
                   int64_t ksk, T* __restrict__ out, const float* __restrict__ lin,
                   const float* __restrict__ tr, const float* __restrict__ nnzs, int64_t total_rows,
-                  int64_t n_rows, int d, int trailing) {
+                  int64_t n_rows, int64_t n_cols, int d, int trailing, int32_t* check) {
     extern __shared__ float smem_q[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t grow = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
@@ -69,7 +86,7 @@ sddmm_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t ksb,
     T* orow = out + grow * trailing;
     for (int j = lane; j < trailing; j += 32) {
         float v = 0.f;
-        if (j < ra.nnz) v = dot_qk<T, kRowContig>(qs, kbh, (int64_t)ra.start + (int64_t)j * ra.stride,
+        if (j < ra.nnz) v = dot_qk<T, kRowContig>(qs, kbh, slot_col(ra, j, n_cols, check, kIndexSddmm),
                                                   d, ksc, ksk);
         orow[j] = DT<T>::from_f(v);
     }
@@ -260,7 +277,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 spmm_rows_kernel(const T* __restrict__ p, const T* __restrict__ v, T* __restrict__ o,
                  const float* __restrict__ lin, const float* __restrict__ tr,
                  const float* __restrict__ nnzs, int64_t total_rows, int64_t n_rows,
-                 int64_t n_cols, int d, int trailing) {
+                 int64_t n_cols, int d, int trailing, int32_t* check) {
     constexpr int V = DT<T>::kVec;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t grow = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
@@ -283,7 +300,7 @@ spmm_rows_kernel(const T* __restrict__ p, const T* __restrict__ v, T* __restrict
             const int t = t0 + g;
             const float pv = __shfl_sync(0xffffffffu, pj, t & 31);
             if (t < lim) {
-                const int64_t col = (int64_t)ra.start + (int64_t)(j0 + t) * ra.stride;
+                const int64_t col = slot_col(ra, j0 + t, n_cols, check, kIndexSpmm);
                 accum_v<T>(acc, pv, vbh + col * d + c0);
             }
         }
@@ -298,7 +315,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 spmm_rows_scalar_kernel(const T* __restrict__ p, const T* __restrict__ v, T* __restrict__ o,
                         const float* __restrict__ lin, const float* __restrict__ tr,
                         const float* __restrict__ nnzs, int64_t total_rows, int64_t n_rows,
-                        int64_t n_cols, int d, int trailing) {
+                        int64_t n_cols, int d, int trailing, int32_t* check) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t grow = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
     if (grow >= total_rows) return;
@@ -310,7 +327,7 @@ spmm_rows_scalar_kernel(const T* __restrict__ p, const T* __restrict__ v, T* __r
     for (int c = lane; c < d; c += 32) {
         float acc = 0.f;
         for (int j = 0; j < nnz; ++j) {
-            const int64_t col = (int64_t)ra.start + (int64_t)j * ra.stride;
+            const int64_t col = slot_col(ra, j, n_cols, check, kIndexSpmm);
             acc = fmaf(DT<T>::to_f(prow[j]), DT<T>::to_f(vbh[col * d + c]), acc);
         }
         o[grow * d + c] = DT<T>::from_f(acc);
@@ -326,7 +343,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t 
                       int64_t ksk, const T* __restrict__ v, T* __restrict__ o,
                       const float* __restrict__ lin, const float* __restrict__ tr,
                       const float* __restrict__ nnzs, int64_t total_rows, int64_t n_rows,
-                      int64_t n_cols, int d, float scale_log2e) {
+                      int64_t n_cols, int d, float scale_log2e, int32_t* check) {
     constexpr int V = DT<T>::kVec;
     extern __shared__ float smem_q[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -346,8 +363,8 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t 
     for (int j0 = 0; j0 < ra.nnz; j0 += 32) {
         const int j = j0 + lane;
         const bool valid = j < ra.nnz;
-        const int64_t col = (int64_t)ra.start + (int64_t)j * ra.stride;
         float sc = -INFINITY;
+        const int64_t col = valid ? slot_col(ra, j, n_cols, check, kIndexFused) : 0;
         if (valid) sc = dot_qk<T, kRowContig>(qs, kbh, col, d, ksc, ksk) * scale_log2e;
         const float m_new = fmaxf(m, warp_max(sc));      // finite: lane 0 of every chunk is valid
         const float corr = exp2f(m - m_new);              // 0 on the first chunk
@@ -361,7 +378,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t 
             const int t = t0 + g;
             const float pv = __shfl_sync(0xffffffffu, pj, t & 31);
             if (t < lim) {
-                const int64_t ct = (int64_t)ra.start + (int64_t)(j0 + t) * ra.stride;
+                const int64_t ct = slot_col(ra, j0 + t, n_cols, check, kIndexFused);
                 accum_v<T>(acc, pv, vbh + ct * d + c0);
             }
         }
@@ -387,7 +404,7 @@ static bool grouped_d_ok(int64_t d, int vec) {
 template <typename T>
 static int32_t sddmm_t(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                        void* out, const float* lin, const float* tr, const float* nnzs, int64_t bh,
-                       int64_t n_rows, int64_t d, int64_t trailing, cudaStream_t st) {
+                       int64_t n_rows, int64_t n_cols, int64_t d, int64_t trailing, cudaStream_t st) {
     const int64_t total = bh * n_rows;
     const unsigned grid = (unsigned)((total + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
@@ -395,12 +412,12 @@ static int32_t sddmm_t(const void* q, const void* k, int64_t ksb, int64_t ksc, i
                         (ksc % DT<T>::kVec == 0) && (ksb % DT<T>::kVec == 0);
     if (contig)
         sddmm_rows_kernel<T, true><<<grid, kWarpsPerBlock * 32, smem, st>>>(
-            (const T*)q, (const T*)k, ksb, ksc, ksk, (T*)out, lin, tr, nnzs, total, n_rows, (int)d,
-            (int)trailing);
+            (const T*)q, (const T*)k, ksb, ksc, ksk, (T*)out, lin, tr, nnzs, total, n_rows, n_cols, (int)d,
+            (int)trailing, g_index_check);
     else
         sddmm_rows_kernel<T, false><<<grid, kWarpsPerBlock * 32, smem, st>>>(
-            (const T*)q, (const T*)k, ksb, ksc, ksk, (T*)out, lin, tr, nnzs, total, n_rows, (int)d,
-            (int)trailing);
+            (const T*)q, (const T*)k, ksb, ksc, ksk, (T*)out, lin, tr, nnzs, total, n_rows, n_cols, (int)d,
+            (int)trailing, g_index_check);
     return launch_status();
 }
 
@@ -435,11 +452,11 @@ static int32_t spmm_t(const void* p, const void* v, void* o, const float* lin, c
     if (grouped_d_ok(d, DT<T>::kVec) && aligned16(v) && aligned16(o))
         spmm_rows_kernel<T><<<grid, kWarpsPerBlock * 32, 0, st>>>(
             (const T*)p, (const T*)v, (T*)o, lin, tr, nnzs, total, n_rows, n_cols, (int)d,
-            (int)trailing);
+            (int)trailing, g_index_check);
     else
         spmm_rows_scalar_kernel<T><<<grid, kWarpsPerBlock * 32, 0, st>>>(
             (const T*)p, (const T*)v, (T*)o, lin, tr, nnzs, total, n_rows, n_cols, (int)d,
-            (int)trailing);
+            (int)trailing, g_index_check);
     return launch_status();
 }
 
@@ -458,11 +475,11 @@ static int32_t attention_t(const void* q, const void* k, int64_t ksb, int64_t ks
     if (contig)
         attention_rows_kernel<T, true><<<grid, kWarpsPerBlock * 32, smem, st>>>(
             (const T*)q, (const T*)k, ksb, ksc, ksk, (const T*)v, (T*)o, lin, tr, nnzs, total,
-            n_rows, n_cols, (int)d, scale * kLog2e);
+            n_rows, n_cols, (int)d, scale * kLog2e, g_index_check);
     else
         attention_rows_kernel<T, false><<<grid, kWarpsPerBlock * 32, smem, st>>>(
             (const T*)q, (const T*)k, ksb, ksc, ksk, (const T*)v, (T*)o, lin, tr, nnzs, total,
-            n_rows, n_cols, (int)d, scale * kLog2e);
+            n_rows, n_cols, (int)d, scale * kLog2e, g_index_check);
     return launch_status();
 }
 
@@ -491,6 +508,11 @@ int32_t attention_generic(const void* q, const void* k, int64_t ksb, int64_t ksc
 
 using namespace splat;
 
+extern "C" int32_t splat_debug_check_indices(int32_t* status_word) {
+    g_index_check = status_word;
+    return SPLAT_OK;
+}
+
 extern "C" int32_t splat_sddmm(const void* q, const void* k, int64_t k_stride_bh,
                                int64_t k_stride_col, int64_t k_stride_k, void* s_out,
                                const float* sTod_lin, const float* sTod_tr, const float* nnzs,
@@ -501,9 +523,9 @@ extern "C" int32_t splat_sddmm(const void* q, const void* k, int64_t k_stride_bh
     if (!q || !k || !s_out || !sTod_lin || !sTod_tr || !nnzs) return SPLAT_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
-        case SPLAT_F32: return sddmm_t<float>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, d, trailing_dim, st);
-        case SPLAT_F16: return sddmm_t<__half>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, d, trailing_dim, st);
-        case SPLAT_BF16: return sddmm_t<__nv_bfloat16>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, d, trailing_dim, st);
+        case SPLAT_F32: return sddmm_t<float>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, trailing_dim, st);
+        case SPLAT_F16: return sddmm_t<__half>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, trailing_dim, st);
+        case SPLAT_BF16: return sddmm_t<__nv_bfloat16>(q, k, k_stride_bh, k_stride_col, k_stride_k, s_out, sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, trailing_dim, st);
         default: return SPLAT_ERR_UNSUPPORTED_DTYPE;
     }
 }
