@@ -162,8 +162,8 @@ def test_auto_path_takes_operands_the_band_path_cannot():
 
 
 def test_launcher_reports_an_earlier_timeout():
-    """The Python launchers keep a pinned mirror of the status word: a launch made after a kernel
-    gave up raises instead of returning an untouched output buffer."""
+    """The Python launchers keep a pinned mirror of the status word: launches made after a kernel
+    gave up raise (within _MIRROR_EVERY launches) instead of returning untouched output buffers."""
     import acsr_helpers as ah
     import splat_native as n
     L, d = 256, 128
@@ -174,10 +174,12 @@ def test_launcher_reports_an_earlier_timeout():
     n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
     torch.cuda.synchronize()
     n.status_word(dev).fill_(5)            # as if a wait had run out inside that kernel
-    n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)  # no-op on the device
-    torch.cuda.synchronize()               # lets the mirror copy land
+    # later launches are no-ops on the device; the mirror is refreshed at least once per
+    # _MIRROR_EVERY launches, so one of them must raise
     with pytest.raises(RuntimeError):
-        n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+        for _ in range(n._MIRROR_EVERY + 2):
+            n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
+            torch.cuda.synchronize()       # lets a mirror copy land
     # the raise cleared the word: back to normal
     n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
     n.check_status_word(0)

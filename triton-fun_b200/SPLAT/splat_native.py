@@ -6,8 +6,10 @@ turns a non-zero status into ``RuntimeError``.  Build the library with
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
+import time
 
 import torch
 
@@ -121,7 +123,7 @@ def mask_row_summary(mask_u8: torch.Tensor) -> torch.Tensor:
 
 def pattern_row_summary(kind: int, n: int, p0: int, p1: int, dev: torch.device) -> torch.Tensor:
     out = torch.empty((4, n), dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_pattern_row_summary(kind, n, p0, p1, out.data_ptr(), _stream(dev)),
               "splat_pattern_row_summary")
     return out
@@ -129,7 +131,7 @@ def pattern_row_summary(kind: int, n: int, p0: int, p1: int, dev: torch.device) 
 
 def pattern_mask(kind: int, n: int, p0: int, p1: int, dev: torch.device) -> torch.Tensor:
     out = torch.empty((n, n), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_pattern_mask_u8(kind, n, p0, p1, out.data_ptr(), out.stride(0) if n else 0,
                                          _stream(dev)), "splat_pattern_mask_u8")
     return out
@@ -143,7 +145,7 @@ def acsr_from_row_summary(rows_i32: torch.Tensor, n_cols: int, block_height: int
     vec = [torch.empty(n_rows, dtype=torch.float32, device=dev) for _ in range(5)]
     spans = [torch.empty(n_blocks, dtype=torch.float32, device=dev) for _ in range(2)]
     td = torch.empty(1, dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_acsr_from_row_summary(
             rows_i32.data_ptr(), n_rows, n_cols, block_height, *[v.data_ptr() for v in vec],
             spans[0].data_ptr(), spans[1].data_ptr(), td.data_ptr(), _stream(dev)),
@@ -163,7 +165,7 @@ def classify(sTod_lin: torch.Tensor, sTod_tr: torch.Tensor, nnzs: torch.Tensor) 
     dev = nnzs.device
     n = nnzs.numel()
     plan = torch.empty(8, dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_acsr_classify(_f32_vec(sTod_lin, n, "sTod_lin"), _f32_vec(sTod_tr, n, "sTod_tr"),
                                        _f32_vec(nnzs, n, "nnzs"), n, plan.data_ptr(), _stream(dev)),
               "splat_acsr_classify")
@@ -194,7 +196,7 @@ def _mirror(dev: torch.device) -> dict:
     m = _STATUS_MIRRORS.get(key)
     if m is None:
         m = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "stream": torch.cuda.Stream(dev),
-             "launched": torch.cuda.Event()}
+             "launched": torch.cuda.Event(), "pending": 0, "stamp": 0.0}
         _STATUS_MIRRORS[key] = m
     return m
 
@@ -216,10 +218,29 @@ def _raise_if_gave_up(dev: torch.device) -> None:
                        "launches are not valid")
 
 
+_MIRROR_EVERY = 32          # launches between two refreshes of the mirror, at most
+_MIRROR_SECONDS = 0.002     # ... or this much time, whichever comes first
+
+
+def _on(dev: torch.device):
+    """Make dev the current device for a library call; free when it already is."""
+    if torch.cuda.current_device() == dev.index:
+        return contextlib.nullcontext()
+    return torch.cuda.device(dev)
+
+
 def _refresh_mirror(dev: torch.device) -> None:
     """After a tensor-core launch: copy the status word to its pinned mirror behind the launch, on
-    a side stream, so the launching stream is not delayed."""
+    a side stream, so the launching stream is not delayed.  Back-to-back launches share a copy (one
+    per _MIRROR_EVERY launches or _MIRROR_SECONDS): a launch that gave up is reported that many
+    launches later at the latest, and the kernels in between do nothing, as documented."""
     m = _mirror(dev)
+    m["pending"] += 1
+    now = time.monotonic()
+    if m["pending"] < _MIRROR_EVERY and now - m["stamp"] < _MIRROR_SECONDS:
+        return
+    m["pending"] = 0
+    m["stamp"] = now
     m["launched"].record(torch.cuda.current_stream(dev))
     m["stream"].wait_event(m["launched"])
     with torch.cuda.stream(m["stream"]):
@@ -323,7 +344,7 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = 
     if _band_candidate(x, path) and k_layout_ok:
         _raise_if_gave_up(dev)
         plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
-        with torch.cuda.device(dev):
+        with _on(dev):
             rc = _lib.splat_sddmm_band(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
                                        _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
                                        _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, trailing_dim,
@@ -340,7 +361,7 @@ def sddmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = 
     if x.dtype != torch.float32 and x.numel() > 0:
         _warn_cuda_core_16bit("sddmm")
     debug = _debug_before(dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_sddmm(x.data_ptr(), y.data_ptr(), ksb, ksc, ksk, output.data_ptr(),
                                _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
                                _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, trailing_dim,
@@ -355,7 +376,7 @@ def softmax(x, output, nnzs, trailing_dim: int, scale: float = 1.0) -> None:
     B, H, L, T = x.shape
     if T != trailing_dim or output.shape != x.shape or output.dtype != x.dtype:
         raise ValueError("softmax: inconsistent operand shapes or dtypes")
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_softmax(x.data_ptr(), output.data_ptr(), _f32_vec(nnzs, L, "nnzs"), B * H,
                                  L, T, float(scale), dtype_code(x.dtype), _stream(dev)),
               "splat_softmax")
@@ -372,7 +393,7 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
     if _band_candidate(x, path):
         _raise_if_gave_up(dev)
         plan_arr = (ctypes.c_int32 * 8)(*classify(sTod_lin, sTod_tr, nnzs))
-        with torch.cuda.device(dev):
+        with _on(dev):
             rc = _lib.splat_spmm_band(x.data_ptr(), y.data_ptr(), output.data_ptr(),
                                       _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
                                       _f32_vec(nnzs, L, "nnzs"), B * H, L, n_cols, d, T,
@@ -389,7 +410,7 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
     if x.dtype != torch.float32 and x.numel() > 0:
         _warn_cuda_core_16bit("spmm")
     debug = _debug_before(dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_spmm(x.data_ptr(), y.data_ptr(), output.data_ptr(),
                               _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
                               _f32_vec(nnzs, L, "nnzs"), B * H, L, n_cols, d, T,
@@ -422,7 +443,7 @@ def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.
     sw = status_word(dev)
     ran = ctypes.c_int32(0)
     _debug_before(dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(_lib.splat_attention_fused_ex(
             q.data_ptr(), kt.data_ptr(), ksb, ksc, ksk, v.data_ptr(), output.data_ptr(),
             _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),

@@ -28,6 +28,7 @@ namespace band {
 using namespace tc;
 
 // defined in attention_band.cu
+bool allow_dynamic_smem(const void* kernel, int bytes);
 bool make_map(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_rows,
               int64_t d, int64_t stride, int box_rows);
 bool make_map_kt(CUtensorMap* map, const void* base, int32_t dtype, int64_t bh, int64_t n_cols,
@@ -723,8 +724,7 @@ static int32_t launch_sddmm(const CUtensorMap& mq, const CUtensorMap& mk, const 
                             cudaStream_t st) {
     using L = SddmmLayout<D>;
     auto kern = sddmm_band_kernel<T, D>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess)
-        return SPLAT_ERR_LAUNCH;
+    if (!allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kSmemBytes)) return SPLAT_ERR_LAUNCH;
     dim3 grid((unsigned)((prm.rows_v + kTile - 1) / kTile), (unsigned)prm.stride, (unsigned)bh);
     kern<<<grid, kThreads, L::kSmemBytes, st>>>(mq, mk, prm);
     return launch_status();
@@ -734,8 +734,7 @@ static int32_t launch_spmm(const CUtensorMap& mv, const CUtensorMap& mo, const P
                            cudaStream_t st) {
     using L = SpmmLayout<D>;
     auto kern = spmm_band_kernel<T, D>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess)
-        return SPLAT_ERR_LAUNCH;
+    if (!allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kSmemBytes)) return SPLAT_ERR_LAUNCH;
     dim3 grid((unsigned)((prm.rows_v + kTile - 1) / kTile), (unsigned)prm.stride, (unsigned)bh);
     kern<<<grid, kThreads, L::kSmemBytes, st>>>(mv, mo, prm);
     return launch_status();
