@@ -178,6 +178,20 @@ int32_t splat_attention_fused_ex(const void* q, const void* k, int64_t k_stride_
                                  int32_t dtype, int32_t path, const int32_t* plan_i32,
                                  int32_t* status_word, int32_t* path_ran, void* stream);
 
+/* splat_attention_fused_ex with the softmax normaliser as a second output: lse (DEVICE fp32,
+ * (BH, n_rows), may be NULL = off) receives, per row, log(sum_j exp(scale * q_i . k_j)) over the
+ * row's non-zeros (natural logarithm; -inf for a row without non-zeros), from either kernel.  It is
+ * what a backward pass over the same tiles recomputes the probabilities from.  Counterpart in the
+ * reference: none -- its module has no gradient path (SPLAT/r_attention.py:12-100) and its softmax
+ * kernel keeps the row maximum and sum in registers only (SPLAT/r_softmax.py:17-58). */
+int32_t splat_attention_fused_lse(const void* q, const void* k, int64_t k_stride_bh,
+                                  int64_t k_stride_col, int64_t k_stride_k, const void* v, void* o,
+                                  float* lse, const float* sTod_lin, const float* sTod_tr,
+                                  const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols,
+                                  int64_t d, float scale, int32_t dtype, int32_t path,
+                                  const int32_t* plan_i32, int32_t* status_word, int32_t* path_ran,
+                                  void* stream);
+
 /* The three-launch chain (SDDMM, softmax in place, SpMM) for callers that cannot allocate device
  * memory -- code running after its host application froze its memory pool, plug-ins that receive
  * input/output buffers but own no allocator, callers that must avoid cudaMalloc's device-wide

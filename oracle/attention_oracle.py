@@ -63,6 +63,16 @@ def softmax_acsr(s: torch.Tensor, meta: dict, scale: float = 1.0) -> torch.Tenso
     return torch.where(den > 0, e / den, torch.zeros_like(e))
 
 
+def lse_acsr(s: torch.Tensor, meta: dict, scale: float = 1.0) -> torch.Tensor:
+    """Per-row log-sum-exp (natural log) of scale*S over slots < nnz_i, (B,H,L) fp32; -inf for rows
+    with nnz 0.  The quantity a backward pass recomputes the probabilities from; the reference keeps
+    it in registers only (SPLAT/r_softmax.py:17-58)."""
+    s = s.float()
+    _cols_, valid = _cols(meta, s.shape[-1])
+    z = torch.where(valid, s * scale, torch.full_like(s, float("-inf")))
+    return torch.logsumexp(z, dim=-1)
+
+
 def spmm_acsr(p: torch.Tensor, v: torch.Tensor, meta: dict) -> torch.Tensor:
     """p (B,H,L,T) in ACSR layout, v (B,H,L,d) -> O (B,H,L,d) fp32."""
     p = p.float()

@@ -214,3 +214,32 @@ def test_bounded_wait_gives_up_and_reports(band_variant):
     n.attention_fused(q, q.transpose(2, 3), q, out, acsr[2], acsr[3], acsr[4], 0.125, n.PATH_BAND)
     n.check_status_word(0)
     assert torch.isfinite(out.float()).all() and not (out == 3.0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_band_log_sum_exp_output(dtype, band_variant):
+    """The optional (B,H,L) fp32 output of the fused call: log-sum-exp of the scaled scores of every
+    row, from each tensor-core kernel -- band rows, rows with a single non-zero (the strided
+    pattern has them), rows without non-zeros would be -inf."""
+    import acsr_helpers as ah
+    import splat_native as n
+    d = 128
+    for i, (kind, L, p0, p1) in enumerate([PATTERNS[0], PATTERNS[2], PATTERNS[4], PATTERNS[6], PATTERNS[8]]):
+        torch.manual_seed(500 + i)
+        acsr = ah.create_acsr(ah.PatternMask(kind, L, p0, p1), 16, 0)
+        meta = ao.metadata_from_pattern(kind, L, p0, p1, 16)
+        q, k, v = (torch.randn(1, 3, L, d).to(dtype) for _ in range(3))
+        out = torch.empty(1, 3, L, d, dtype=dtype, device="cuda")
+        lse = torch.full((1, 3, L), float("nan"), dtype=torch.float32, device="cuda")
+        scale = d ** -0.5
+        n.attention_fused(q.cuda(), k.cuda().transpose(2, 3), v.cuda(), out, acsr[2], acsr[3], acsr[4], scale,
+                          n.PATH_BAND, lse=lse)
+        n.check_status_word(0)
+        s = at.sddmm_acsr(q, k.transpose(2, 3), meta, meta["trailing_dim"])
+        ref = at.lse_acsr(s, meta, scale)
+        got = lse.cpu()
+        assert torch.isfinite(got).all(), f"pattern {(kind, L, p0, p1)}: non-finite lse"
+        err = (got - ref).abs().max().item()
+        assert err < 2e-2, f"pattern {(kind, L, p0, p1)} {dtype}: lse max abs err {err}"
+        assert_close(out, at.attention_acsr(q, k.transpose(2, 3), v, meta, meta["trailing_dim"], scale), dtype,
+                     f"output with lse, pattern {(kind, L, p0, p1)}")

@@ -290,3 +290,34 @@ def test_checked_index_mode_clamps_and_reports():
     for got, want, name in zip((s_u, o1_u, o2_u), ref, ("sddmm", "spmm", "fused")):
         assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), f"unchecked {name}: {(got - want).abs().max().item()}"
     assert (s_c - s_u).abs().max().item() > 1e-3   # the clamp changed what was read
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_fused_generic_log_sum_exp(golden_meta, dtype):
+    """lse output of the CUDA-core fused kernel, including rows without non-zeros (-inf)."""
+    import acsr_helpers as ah
+    import r_attention
+    import splat_native as n
+    L, d = 192, 64
+    mask = ah.create_windowed_mask(L, 20)
+    attn = r_attention.RegularAttention(2, L, 2, d, mask, 16, 16, 0, dtype, scale=0.2, path=n.PATH_GENERIC, lse=True)
+    # empty rows: zero their nnz
+    attn.nnzs[5] = 0
+    attn.nnzs[100] = 0
+    torch.manual_seed(21)
+    q, k, v = (torch.randn(2, 2, L, d).to(dtype) for _ in range(3))
+    out = attn([q.cuda(), k.cuda().transpose(2, 3), v.cuda()])
+    torch.cuda.synchronize()
+    meta = ao.metadata_from_pattern(ao.PATTERN_WINDOWED, L, 20, 0, 16)
+    meta = dict(meta)
+    nn = np.array(meta["nnzs"], dtype=np.float32).copy(); nn[5] = 0; nn[100] = 0
+    meta["nnzs"] = nn
+    s = at.sddmm_acsr(q, k.transpose(2, 3), meta, meta["trailing_dim"])
+    ref = at.lse_acsr(s, meta, 0.2)
+    got = attn.lse.cpu()
+    assert torch.isinf(got[:, :, 5]).all() and (got[:, :, 5] < 0).all()
+    assert torch.isinf(got[:, :, 100]).all()
+    keep = torch.isfinite(ref)
+    tol = 1e-4 if dtype == torch.float32 else 5e-3
+    assert (got[keep] - ref[keep]).abs().max().item() < tol
+    assert_close(out, at.attention_acsr(q, k.transpose(2, 3), v, meta, meta["trailing_dim"], 0.2), dtype, "generic with lse")

@@ -31,7 +31,11 @@ class RegularAttention(nn.Module):
 
     def __init__(self, batch: int, seq_length: int, num_heads: int, head_dim: int, mask,
                  BLOCK_SIZE_Y: int, BLOCK_SIZE_X: int, GPU_ID: Any, out_dtype: torch.dtype, *,
-                 scale: float = 1.0, fused: bool = True, path: int = _n.PATH_AUTO):
+                 scale: float = 1.0, fused: bool = True, path: int = _n.PATH_AUTO, lse: bool = False):
+        """Positional parameters as in the reference (SPLAT/r_attention.py:14-16).  Keyword-only
+        additions: scale (softmax scale, the reference applies none), fused (one kernel instead of
+        the three launches), path (kernel selection), lse (fused path only: keep a float32 (B,H,L)
+        buffer self.lse that every forward fills with the rows' log-sum-exp of the scaled scores)."""
         super().__init__()
         self.device = _n.resolve_device(GPU_ID)
         self.scale, self.fused, self.path = float(scale), bool(fused), int(path)
@@ -48,6 +52,10 @@ class RegularAttention(nn.Module):
         self.BLOCK_SIZE_Y = BLOCK_SIZE_Y
         self.BLOCK_SIZE_X = BLOCK_SIZE_X
 
+        if lse and not self.fused:
+            raise ValueError("lse=True needs the fused path (the three launches keep no row sums)")
+        self.lse = (torch.empty((batch, num_heads, seq_length), dtype=torch.float32, device=self.device)
+                    if lse else None)
         self.rsddmm_output = self.rsoftmax_output = None
         self.rsddmm_grid_dim = self.rsddmm_tb_map_x = self.rsddmm_tb_map_y = None
         self.rsoftmax_grid_dim = self.rsoftmax_trailing_dim_pow_two = None
@@ -75,7 +83,8 @@ class RegularAttention(nn.Module):
         q, k, v = x
         if self.fused:
             _n.attention_fused(q, k, v, self.rspmm_output, self.sTod_linear_transformations,
-                               self.sTod_translations, self.nnzs, self.scale, self.path, self.plan)
+                               self.sTod_translations, self.nnzs, self.scale, self.path, self.plan,
+                               lse=self.lse)
             return self.rspmm_output
         if self.rsddmm_output is None:
             self._unfused_preambles()

@@ -41,6 +41,8 @@ SIGNATURES = {
                               _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp],
     "splat_attention_fused_ex": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                  _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp, _vp],
+    "splat_attention_fused_lse": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                  _i64, _i64, _f32, _i32, _i32, _vp, _vp, _vp, _vp],
     "splat_sddmm_band": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
                          _i32, _vp, _vp, _vp],
     "splat_spmm_band": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp,
@@ -420,10 +422,11 @@ def spmm(x, y, output, sTod_lin, sTod_tr, nnzs, trailing_dim: int, path: int = P
 
 
 def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.0,
-                    path: int = PATH_AUTO, plan=None) -> None:
+                    path: int = PATH_AUTO, plan=None, lse=None) -> None:
     """q, v, output (B,H,L,d) contiguous; kt (B,H,d,L) -- contiguous (the reference's layout), or
     the transposed view of a contiguous (B,H,L,d) tensor.  The tensor-core path takes both (the
-    contiguous one for stride-1 patterns)."""
+    contiguous one for stride-1 patterns).  lse: optional contiguous float32 (B,H,L) tensor that
+    receives each row's log-sum-exp of the scaled scores (natural log, -inf for empty rows)."""
     dev = q.device
     _contig(q, "q"); _contig(v, "v"); _contig(output, "output")
     B, H, L, d = q.shape
@@ -432,6 +435,9 @@ def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.
     if kt.shape[2] != d or tuple(v.shape) != (B, H, n_cols, d) or output.shape != q.shape or \
             len({q.dtype, kt.dtype, v.dtype, output.dtype}) != 1:
         raise ValueError("attention: inconsistent operand shapes or dtypes")
+    if lse is not None and (lse.dtype != torch.float32 or tuple(lse.shape) != (B, H, L) or
+                            not lse.is_contiguous() or lse.device != dev):
+        raise ValueError("attention: lse must be a contiguous float32 (B, H, L) tensor on the operands' device")
     plan_arr = None
     tensor_core = _band_candidate(q, path)      # a tensor-core kernel may run (the library decides)
     if path != PATH_GENERIC:
@@ -444,12 +450,13 @@ def attention_fused(q, kt, v, output, sTod_lin, sTod_tr, nnzs, scale: float = 1.
     ran = ctypes.c_int32(0)
     _debug_before(dev)
     with _on(dev):
-        check(_lib.splat_attention_fused_ex(
+        check(_lib.splat_attention_fused_lse(
             q.data_ptr(), kt.data_ptr(), ksb, ksc, ksk, v.data_ptr(), output.data_ptr(),
+            lse.data_ptr() if lse is not None and lse.numel() > 0 else None,
             _f32_vec(sTod_lin, L, "sTod_lin"), _f32_vec(sTod_tr, L, "sTod_tr"),
             _f32_vec(nnzs, L, "nnzs"), bh, L, n_cols, d, float(scale), dtype_code(q.dtype),
             int(path), ctypes.cast(plan_arr, _vp) if plan_arr is not None else None,
-            sw.data_ptr(), ctypes.byref(ran), _stream(dev)), "splat_attention_fused_ex")
+            sw.data_ptr(), ctypes.byref(ran), _stream(dev)), "splat_attention_fused_lse")
     if ran.value == PATH_BAND:
         _refresh_mirror(dev)
     elif q.dtype != torch.float32 and q.numel() > 0 and path == PATH_AUTO:

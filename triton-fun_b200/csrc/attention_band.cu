@@ -77,6 +77,9 @@ struct Params {
     const float* nnzs;
     const void* v;
     void* o;
+    const void* q;     // raw operands: only the single score of a row with one non-zero is read through
+    const void* k;     //   them (log-sum-exp output); everything else goes through the tensor maps
+    float* lse;        // (BH, L) natural-log log-sum-exp of every row, or null
     int32_t* status;
     int64_t n_rows;    // L
     int rows_v;        // L / stride: rows of one residue class
@@ -147,7 +150,23 @@ __device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) 
         if (clock64() - t0 > 200000000LL) break;
 }
 
+// Natural-log log-sum-exp of a row: from the running maximum and sum of a band row (log2 domain), the
+// one score scale * q_i . k_start of a row with a single non-zero (computed here from the raw
+// operands; such rows are outside the band), -inf for a row without non-zeros.
 template <typename T, int D>
+__device__ __forceinline__ float row_lse(const Params& p, int64_t bh, int64_t row_real, int row_nnz, int row_start,
+                                         float m_used, float l_sum) {
+    if (row_nnz > 1) return lse_from_log2(m_used, l_sum);
+    if (row_nnz != 1) return -INFINITY;
+    const T* qr = reinterpret_cast<const T*>(p.q) + (bh * p.n_rows + row_real) * D;
+    const T* kb = reinterpret_cast<const T*>(p.k);
+    // K[bh][start][c]: rows of d elements, or column `start` of the (d, L) array
+    const float s = p.kt_major ? dot_strided<T>(qr, kb + bh * p.n_rows * D + row_start, p.n_rows, D)
+                               : dot_strided<T>(qr, kb + (bh * p.n_rows + row_start) * D, 1, D);
+    return s * p.scale_log2 * kLn2;
+}
+
+template <typename T, int D, bool kLse>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -534,6 +553,8 @@ attention_band_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         uint8_t* s_o = s_q + x * L::kTileBytes;
         const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+        if (kLse && row_real >= 0 && ok)   // (the instantiation without this output is the default)
+            p.lse[bh * p.n_rows + row_real] = row_lse<T, D>(p, bh, row_real, row_nnz, row_start, m_used, l_sum);
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
             if (have_o && ok) {  // warp-uniform
@@ -612,7 +633,7 @@ template <int D> struct Layout1 {
     static constexpr int kSmemBytes = kCtrlOff + (int)sizeof(Control1) + 1024;
 };
 
-template <typename T, int D>
+template <typename T, int D, bool kLse>
 __global__ void __launch_bounds__(kThreads1, 2)
 attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -907,6 +928,8 @@ attention_band1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int t = warp * 32 + lane;
         const T* vrow = reinterpret_cast<const T*>(p.v) + (bh * p.n_rows + (int64_t)row_start) * D;
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+        if (kLse && row_real >= 0 && ok)   // (the instantiation without this output is the default)
+            p.lse[bh * p.n_rows + row_real] = row_lse<T, D>(p, bh, row_real, row_nnz, row_start, m_used, l_sum);
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
             if (have_o && ok) {
@@ -1078,7 +1101,7 @@ template <typename T, int D>
 static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                       const CUtensorMap& mo, const Params& prm, int64_t bh, cudaStream_t st) {
     using L = Layout<D>;
-    auto kern = attention_band_kernel<T, D>;
+    auto kern = prm.lse != nullptr ? attention_band_kernel<T, D, true> : attention_band_kernel<T, D, false>;
     if (!allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kSmemBytes)) return SPLAT_ERR_LAUNCH;
     const int pairs = (prm.rows_v + 2 * kTile - 1) / (2 * kTile);
     dim3 grid((unsigned)pairs, (unsigned)prm.stride, (unsigned)bh);
@@ -1090,7 +1113,7 @@ template <typename T, int D>
 static int32_t launch1(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                        const CUtensorMap& mo, const Params& prm, int64_t bh, cudaStream_t st) {
     using L = Layout1<D>;
-    auto kern = attention_band1_kernel<T, D>;
+    auto kern = prm.lse != nullptr ? attention_band1_kernel<T, D, true> : attention_band1_kernel<T, D, false>;
     if (!allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kSmemBytes)) return SPLAT_ERR_LAUNCH;
     const int tiles = (prm.rows_v + kTile - 1) / kTile;
     dim3 grid((unsigned)tiles, (unsigned)prm.stride, (unsigned)bh);
@@ -1117,13 +1140,13 @@ static int32_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 int32_t attention_pair(const void* q, const void* k, int kt_major, const void* v, void* o,
                        const float* lin, const float* tr, const float* nnzs, int64_t bh, int64_t n_rows,
                        int64_t stride, float scale, int32_t dtype, int32_t* status_word, int max_pairs,
-                       cudaStream_t st);
+                       float* lse, cudaStream_t st);
 
 int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                        const void* v, void* o, const float* lin, const float* tr,
                        const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                        float scale, int32_t dtype, const int32_t* plan, int32_t* status_word,
-                       cudaStream_t st) {
+                       float* lse, cudaStream_t st) {
     if (bh < 0 || n_rows < 0) return SPLAT_ERR_BAD_ARG;
     if (bh == 0 || n_rows == 0) return SPLAT_ERR_UNSUPPORTED_SHAPE;   // empty: left to the generic path
     if (!q || !k || !v || !o || !lin || !tr || !nnzs || !plan || !status_word)
@@ -1161,7 +1184,7 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
         int max_pairs = 0;
         if (const char* e = getenv("SPLAT_B200_PAIR_MAX")) max_pairs = atoi(e);
         const int32_t rc = attention_pair(q, k, kt_major ? 1 : 0, v, o, lin, tr, nnzs, bh, n_rows, stride,
-                                          scale, dtype, status_word, max_pairs, st);
+                                          scale, dtype, status_word, max_pairs, lse, st);
         if (rc != SPLAT_ERR_UNSUPPORTED_SHAPE) return rc;
     }
     if (variant == 3) variant = 2;
@@ -1177,6 +1200,7 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     band::Params prm;
     prm.kt_major = kt_major ? 1 : 0;
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.o = o; prm.status = status_word;
+    prm.q = q; prm.k = k; prm.lse = lse;
     prm.n_rows = n_rows; prm.rows_v = (int)(n_rows / stride); prm.stride = (int)stride;
     prm.scale_log2 = scale * kLog2e;
 #ifdef SPLAT_BAND_TRACE

@@ -95,6 +95,9 @@ struct Params {
     const float* tr;
     const float* nnzs;
     const void* v;
+    const void* q;         // raw operands: only the single score of a row with one non-zero is read
+    const void* k;         //   through them (log-sum-exp output)
+    float* lse;            // (BH, L) natural-log log-sum-exp of every row, or null
     int32_t* status;
     long long* trace;      // profiling builds only (else null)
     int64_t n_rows;        // L
@@ -759,6 +762,22 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const float l_sum = a0 * ml0.y + a1 * ml1.y;
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             const float w0 = a0 * inv, w1 = a1 * inv;
+            if (p.lse != nullptr && row_exists) {
+                // band rows from the merged maximum and sum; a row with one non-zero from its single
+                // score (outside the band, read from the raw operands); -inf without non-zeros
+                const int64_t row_real = (int64_t)u_own * p.stride + res;
+                float val = -INFINITY;
+                if (row_nnz > 1) {
+                    val = lse_from_log2(m, l_sum);
+                } else if (row_nnz == 1) {
+                    const T* qr = reinterpret_cast<const T*>(p.q) + (bh * p.n_rows + row_real) * D;
+                    const T* kb = reinterpret_cast<const T*>(p.k);
+                    const float s = p.kt_major ? dot_strided<T>(qr, kb + bh * p.n_rows * D + row_start, p.n_rows, D)
+                                               : dot_strided<T>(qr, kb + (bh * p.n_rows + row_start) * D, 1, D);
+                    val = s * p.scale_log2 * kLn2;
+                }
+                p.lse[bh * p.n_rows + row_real] = val;
+            }
             // This warp's rows of O are final once the PV of its last step with valid columns has
             // completed; later steps of the item (the other tile's) add zeros to them.  A warp
             // without such a step still waits for the item's first PV: that MMA is only issued once
@@ -930,7 +949,7 @@ static int32_t launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 int32_t attention_pair(const void* q, const void* k, int kt_major, const void* v, void* o,
                        const float* lin, const float* tr, const float* nnzs, int64_t bh, int64_t n_rows,
                        int64_t stride, float scale, int32_t dtype, int32_t* status_word, int max_pairs,
-                       cudaStream_t st) {
+                       float* lse, cudaStream_t st) {
     const int64_t d = pair::D;
     const int64_t rows_v = n_rows / stride;
     const int64_t items_per_class = (rows_v + pair::kItemRows - 1) / pair::kItemRows;
@@ -945,6 +964,7 @@ int32_t attention_pair(const void* q, const void* k, int kt_major, const void* v
         return SPLAT_ERR_DRIVER;
     pair::Params prm;
     prm.lin = lin; prm.tr = tr; prm.nnzs = nnzs; prm.v = v; prm.status = status_word;
+    prm.q = q; prm.k = k; prm.lse = lse;
     prm.trace = pair::g_trace;
     prm.kt_major = kt_major;
     prm.n_rows = n_rows;

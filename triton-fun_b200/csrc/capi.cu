@@ -7,13 +7,13 @@ namespace splat {
 int32_t attention_generic(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                           const void* v, void* o, const float* lin, const float* tr,
                           const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
-                          float scale, int32_t dtype, cudaStream_t st);
+                          float scale, int32_t dtype, float* lse, cudaStream_t st);
 // Returns SPLAT_ERR_UNSUPPORTED_SHAPE (and launches nothing) when the problem does not qualify.
 int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                        const void* v, void* o, const float* lin, const float* tr,
                        const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
                        float scale, int32_t dtype, const int32_t* plan, int32_t* status_word,
-                       cudaStream_t st);
+                       float* lse, cudaStream_t st);
 }  // namespace splat
 
 namespace splat {
@@ -56,13 +56,13 @@ extern "C" const char* splat_status_string(int32_t status) {
     }
 }
 
-extern "C" int32_t splat_attention_fused_ex(const void* q, const void* k, int64_t k_stride_bh,
-                                            int64_t k_stride_col, int64_t k_stride_k, const void* v,
-                                            void* o, const float* sTod_lin, const float* sTod_tr,
-                                            const float* nnzs, int64_t bh, int64_t n_rows,
-                                            int64_t n_cols, int64_t d, float scale, int32_t dtype,
-                                            int32_t path, const int32_t* plan_i32,
-                                            int32_t* status_word, int32_t* path_ran, void* stream) {
+extern "C" int32_t splat_attention_fused_lse(const void* q, const void* k, int64_t k_stride_bh,
+                                             int64_t k_stride_col, int64_t k_stride_k, const void* v,
+                                             void* o, float* lse, const float* sTod_lin,
+                                             const float* sTod_tr, const float* nnzs, int64_t bh,
+                                             int64_t n_rows, int64_t n_cols, int64_t d, float scale,
+                                             int32_t dtype, int32_t path, const int32_t* plan_i32,
+                                             int32_t* status_word, int32_t* path_ran, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (path_ran) *path_ran = SPLAT_PATH_AUTO;   // nothing launched yet
     if (path != SPLAT_PATH_AUTO && path != SPLAT_PATH_GENERIC && path != SPLAT_PATH_BAND)
@@ -70,7 +70,7 @@ extern "C" int32_t splat_attention_fused_ex(const void* q, const void* k, int64_
     if (path != SPLAT_PATH_GENERIC && plan_i32 != nullptr && status_word != nullptr) {
         int32_t rc = splat::attention_band(q, k, k_stride_bh, k_stride_col, k_stride_k, v, o,
                                            sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, scale,
-                                           dtype, plan_i32, status_word, st);
+                                           dtype, plan_i32, status_word, lse, st);
         // Under SPLAT_PATH_AUTO a tensor-core path that does not apply -- shape, alignment of the
         // caller's buffers, or a driver without tensor-map support -- hands over to the general
         // kernel, which takes any operands; asked for explicitly, it reports why it cannot run.
@@ -85,9 +85,21 @@ extern "C" int32_t splat_attention_fused_ex(const void* q, const void* k, int64_
     }
     const int32_t rc = splat::attention_generic(q, k, k_stride_bh, k_stride_col, k_stride_k, v, o,
                                                 sTod_lin, sTod_tr, nnzs, bh, n_rows, n_cols, d, scale,
-                                                dtype, st);
+                                                dtype, lse, st);
     if (rc == SPLAT_OK && path_ran && bh > 0 && n_rows > 0) *path_ran = SPLAT_PATH_GENERIC;
     return rc;
+}
+
+extern "C" int32_t splat_attention_fused_ex(const void* q, const void* k, int64_t k_stride_bh,
+                                            int64_t k_stride_col, int64_t k_stride_k, const void* v,
+                                            void* o, const float* sTod_lin, const float* sTod_tr,
+                                            const float* nnzs, int64_t bh, int64_t n_rows,
+                                            int64_t n_cols, int64_t d, float scale, int32_t dtype,
+                                            int32_t path, const int32_t* plan_i32,
+                                            int32_t* status_word, int32_t* path_ran, void* stream) {
+    return splat_attention_fused_lse(q, k, k_stride_bh, k_stride_col, k_stride_k, v, o, nullptr, sTod_lin,
+                                     sTod_tr, nnzs, bh, n_rows, n_cols, d, scale, dtype, path, plan_i32,
+                                     status_word, path_ran, stream);
 }
 
 extern "C" int32_t splat_attention_fused(const void* q, const void* k, int64_t k_stride_bh,

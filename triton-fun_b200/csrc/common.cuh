@@ -111,5 +111,19 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline int elem_size(int32_t dtype) { return dtype == SPLAT_F32 ? 4 : 2; }
 
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Natural-log log-sum-exp of a row from its running maximum m and sum l = sum_j 2^(s_j - m), both in
+// the log2 domain (scores already multiplied by scale * log2 e); -inf for a row without non-zeros.
+__device__ __forceinline__ float lse_from_log2(float m, float l) {
+    return l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+}
+// dot(a[0..d), b[0], b[stride], ...) in fp32: the single score of a row with one non-zero.
+template <typename T>
+__device__ __forceinline__ float dot_strided(const T* a, const T* b, int64_t b_stride, int d) {
+    float acc = 0.f;
+    for (int c = 0; c < d; ++c) acc = fmaf(DT<T>::to_f(a[c]), DT<T>::to_f(b[(int64_t)c * b_stride]), acc);
+    return acc;
+}
 
 }  // namespace splat

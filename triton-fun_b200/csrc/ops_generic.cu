@@ -343,7 +343,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t 
                       int64_t ksk, const T* __restrict__ v, T* __restrict__ o,
                       const float* __restrict__ lin, const float* __restrict__ tr,
                       const float* __restrict__ nnzs, int64_t total_rows, int64_t n_rows,
-                      int64_t n_cols, int d, float scale_log2e, int32_t* check) {
+                      int64_t n_cols, int d, float scale_log2e, int32_t* check, float* lse) {
     constexpr int V = DT<T>::kVec;
     extern __shared__ float smem_q[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -384,6 +384,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t 
         }
     }
     reduce_groups<V>(acc, lpg);
+    if (lse != nullptr && lane == 0) lse[grow] = lse_from_log2(m, l);
     if (g == 0) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -464,7 +465,7 @@ template <typename T>
 static int32_t attention_t(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                            const void* v, void* o, const float* lin, const float* tr,
                            const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
-                           float scale, cudaStream_t st) {
+                           float scale, float* lse, cudaStream_t st) {
     if (!grouped_d_ok(d, DT<T>::kVec) || !aligned16(v) || !aligned16(o))
         return SPLAT_ERR_UNSUPPORTED_SHAPE;
     const int64_t total = bh * n_rows;
@@ -475,11 +476,11 @@ static int32_t attention_t(const void* q, const void* k, int64_t ksb, int64_t ks
     if (contig)
         attention_rows_kernel<T, true><<<grid, kWarpsPerBlock * 32, smem, st>>>(
             (const T*)q, (const T*)k, ksb, ksc, ksk, (const T*)v, (T*)o, lin, tr, nnzs, total,
-            n_rows, n_cols, (int)d, scale * kLog2e, g_index_check);
+            n_rows, n_cols, (int)d, scale * kLog2e, g_index_check, lse);
     else
         attention_rows_kernel<T, false><<<grid, kWarpsPerBlock * 32, smem, st>>>(
             (const T*)q, (const T*)k, ksb, ksc, ksk, (const T*)v, (T*)o, lin, tr, nnzs, total,
-            n_rows, n_cols, (int)d, scale * kLog2e, g_index_check);
+            n_rows, n_cols, (int)d, scale * kLog2e, g_index_check, lse);
     return launch_status();
 }
 
@@ -492,14 +493,14 @@ static bool sizes_ok(int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d, int6
 int32_t attention_generic(const void* q, const void* k, int64_t ksb, int64_t ksc, int64_t ksk,
                           const void* v, void* o, const float* lin, const float* tr,
                           const float* nnzs, int64_t bh, int64_t n_rows, int64_t n_cols, int64_t d,
-                          float scale, int32_t dtype, cudaStream_t st) {
+                          float scale, int32_t dtype, float* lse, cudaStream_t st) {
     if (!sizes_ok(bh, n_rows, n_cols, d, 0)) return SPLAT_ERR_BAD_ARG;
     if (bh * n_rows == 0) return SPLAT_OK;   // empty batch: nothing to read or write, pointers may be null
     if (!q || !k || !v || !o || !lin || !tr || !nnzs) return SPLAT_ERR_BAD_ARG;
     switch (dtype) {
-        case SPLAT_F32: return attention_t<float>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, st);
-        case SPLAT_F16: return attention_t<__half>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, st);
-        case SPLAT_BF16: return attention_t<__nv_bfloat16>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, st);
+        case SPLAT_F32: return attention_t<float>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, lse, st);
+        case SPLAT_F16: return attention_t<__half>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, lse, st);
+        case SPLAT_BF16: return attention_t<__nv_bfloat16>(q, k, ksb, ksc, ksk, v, o, lin, tr, nnzs, bh, n_rows, n_cols, d, scale, lse, st);
         default: return SPLAT_ERR_UNSUPPORTED_DTYPE;
     }
 }
