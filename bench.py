@@ -204,6 +204,10 @@ def torch_dense_masked_baseline(cfgs=(1, 2), budget_s=12.0):
     return out
 
 
+# fused band kernel by the library's SPLAT_B200_BAND_TILES switch (default: one Q tile per CTA)
+BAND_KERNELS = {"1": "attention_band1_kernel", "2": "attention_band_kernel", "3": "attention_pair_kernel"}
+
+
 def ncu_traffic(cfg, heads, path):
     """DRAM bytes per launch of the fused kernel from the ncu captures summarised under
     profiles/ (dram__bytes_read.sum + dram__bytes_write.sum), scaled by the head count, with the
@@ -211,6 +215,8 @@ def ncu_traffic(cfg, heads, path):
     meta_path = os.path.join(ROOT, "profiles", "dram_traffic.md")
     if path != "band" or not os.path.exists(meta_path):
         return None, None
+    if os.environ.get("SPLAT_B200_BAND_TILES", "1")[:1] != "1":
+        return None, "the traffic record covers the default kernel only"
     with open(meta_path) as f:
         text = f.read()
     try:
@@ -544,7 +550,8 @@ def run_ours(args):
                                                          "ncu capture scaled by heads)",
                      "traffic_source": traffic_source,
                      "kernel": "sddmm + softmax + spmm (three launches)" if unfused else
-                               ("attention_band_kernel" if args.path == "band" else "attention_rows_kernel"),
+                               (BAND_KERNELS.get(os.environ.get("SPLAT_B200_BAND_TILES", "1")[:1], "attention_band1_kernel")
+                                if args.path == "band" else "attention_rows_kernel"),
                      "peak_source": peaks["source"],
                      "peak_kind": "burst", "launch_ms": launch_ms, "launch_ms_median": launch_ms_median,
                      "launch_ms_best": launch_ms_best,

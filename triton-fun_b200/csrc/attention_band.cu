@@ -1170,14 +1170,13 @@ int32_t attention_band(const void* q, const void* k, int64_t ksb, int64_t ksc, i
     if (!k_major && (stride != 1 || n_cols % 8 != 0)) return SPLAT_ERR_UNSUPPORTED_SHAPE;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SPLAT_ERR_MISALIGNED;
 
-    // Kernel choice.  1: one Q tile per CTA (two CTAs per SM), for classes with a single row tile or
-    // problems too small to fill the GPU with larger units (per-CTA prologue and epilogue are not
-    // overlapped in the other kernels' first wave).  3: persistent CTA pairs (attention_pair.cu),
-    // d = 128 only.  2: two Q tiles per CTA, the remaining large problems (d = 64).
-    // SPLAT_B200_BAND_TILES=1|2|3 overrides; SPLAT_B200_PAIR_MAX limits the resident pairs of 3.
-    const int64_t rows_v = n_rows / stride;
-    const int64_t pair_items = ((rows_v + 2 * band::kTile - 1) / (2 * band::kTile)) * stride * bh;
-    int variant = (rows_v <= band::kTile || pair_items < 16 * 148) ? 1 : 2;
+    // Kernel choice.  1 (default): one Q tile per CTA, two CTAs per SM -- measured the fastest of the
+    // three on every shape tried (5 % ahead of the two-tile kernel on 64 to 256 heads of
+    // L = 32768, d = 128, window 1024; level with it on all 512, where both sit at the power cap;
+    // 8 % ahead at d = 64).  2: two Q tiles per CTA sharing every K/V tile (half the L2 -> SM
+    // traffic).  3: persistent CTA pairs (attention_pair.cu), d = 128 only.
+    // SPLAT_B200_BAND_TILES=1|2|3 selects; SPLAT_B200_PAIR_MAX limits the resident pairs of 3.
+    int variant = 1;
     if (const char* e = getenv("SPLAT_B200_BAND_TILES"))
         if (e[0] >= '1' && e[0] <= '3') variant = e[0] - '0';
     if (variant == 3 && d == 128) {
